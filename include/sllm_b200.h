@@ -458,6 +458,7 @@ typedef struct {
     float softcap;           /* > 0: score <- softcap * tanh(score / softcap), after the scale */
     const float* slopes;     /* [heads] or NULL: score <- score - slopes[h] * (i - j), after the cap */
     int32_t values_in_keys;  /* != 0: a value row is the first dv columns of the key row (one pool; v_pool is not read) */
+    const float* logdist;    /* [2][heads] or NULL: score <- score - r1[h] * ln(1 + r2[h] * (i - j)) with r1 = row 0, r2 = row 1 */
 } sllm_seq_attn_opts;
 /* Causal softmax attention of every token over positions 0..pos of its own sequence: score = (q . k) * scale, query head h reads
  * key/value head h / (heads / kv_heads). Keys are visited in tiles of 32, cut into nsplit interleaved shares; the partial results
@@ -475,17 +476,61 @@ int sllm_seq_attention_finish(const sllm_seq_batch* b, const float* ws, int32_t 
 /* Heads scaled to unit root mean square and the cache write, for mixers without rotation: bit 0 of `unit` = every query head of q (in
  * place), bit 1 = every key head, bit 2 = every value head is divided by sqrt(mean(head^2) + eps). share 1: the values (after the
  * division) are also kept in v_shared [T][kv_heads*dv]; share 2: v <- (1 - lambda) * v + lambda * v_shared (what an earlier layer kept
- * for the same tokens). k and v go to their pools at (page of pos, kv head, pos % page_len). */
+ * for the same tokens). k and v go to their pools at (page of pos, kv head, pos % page_len). q_temp_every > 0: every query is also
+ * multiplied by 1 + q_temp_coef * ln(floor((pos + 1) / q_temp_every) + 1), a temperature that grows with the position. */
 int sllm_seq_unit_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t heads, int32_t dk, const float* k, int32_t ldk,
                      int32_t kv_heads, const float* v, int32_t ldv, int32_t dv, float eps, int32_t unit, float* v_shared, int32_t share,
-                     float lambda, void* k_pool, void* v_pool, int32_t kv_dtype, sllm_stream_t stream);
+                     float lambda, void* k_pool, void* v_pool, int32_t kv_dtype, float q_temp_coef, int32_t q_temp_every, sllm_stream_t stream);
 /* Latent attention's cache write: low [T][rank + dr] is one token's low-rank row; its first `rank` entries, RMS-normed with norm_w, and
  * its last dr entries, the first 2*n_freq of them rotated by pos * freq[i] (interleaved pairs, angles in double), form the pool row
  * [pages][1][page_len][rank + dr]. q [T][heads][dn + dr]: the dr-part of every head is rotated the same way and stored at
- * q_out[t][h][rank ..] (q_out rows of heads * (rank + dr); the first `rank` columns of a head belong to the absorbed query). */
+ * q_out[t][h][rank ..] (q_out rows of heads * (rank + dr); the first `rank` columns of a head belong to the absorbed query). cos and sin
+ * are multiplied by `magnitude`. low NULL: nothing is cached (the layer attends over another layer's rows), only the queries turn. */
 int sllm_seq_latent_kv(const sllm_seq_batch* b, const float* q, int32_t ldq, int32_t heads, int32_t dn, int32_t dr, const float* low,
                        int32_t ldlow, int32_t rank, const float* norm_w, float eps, const double* freq, int32_t n_freq, float* q_out,
-                       int32_t ldqo, void* pool, int32_t kv_dtype, sllm_stream_t stream);
+                       int32_t ldqo, void* pool, int32_t kv_dtype, float magnitude, sllm_stream_t stream);
+/* ---- blocks of models whose sublayers sit between scalar RMS norms and read through a short convolution; the gated delta rule; a
+ * mixture of experts ---- */
+/* out[t] = table[ids[t]] + pairs[row], row = (prev_ids[t] * mul_prev + ids[t] * mul_cur) mod buckets, or row `buckets` (the last of the
+ * buckets + 1 rows) when prev_ids[t] < 0: the sequence's first token */
+int sllm_seq_embed_pair(const int32_t* ids, const int32_t* prev_ids, const void* table, const void* pairs, int32_t w_dtype, int32_t vocab,
+                        int32_t d, int32_t buckets, int64_t mul_prev, int64_t mul_cur, float* out, int32_t T, sllm_stream_t stream);
+/* y = x / sqrt(mean(x^2) + eps) * w per row of n floats (w NULL = no weight) */
+int sllm_seq_rmsnorm_rows(const float* x, int32_t ldx, const float* w, float eps, float* y, int32_t ldy, int32_t T, int32_t n,
+                          sllm_stream_t stream);
+/* out = act(gate) * up (act 0 = silu); out fp32 [T][ldo] and / or out16 dense bf16 [T][n] (the operand of a tensor-core product) */
+int sllm_seq_gated_act(const float* gate, int32_t ldg, const float* up, int32_t ldu, int32_t act, float* out, int32_t ldo, void* out16,
+                       int32_t T, int32_t n, sllm_stream_t stream);
+/* x <- cap * tanh(x / cap) over n floats */
+int sllm_seq_softcap(float* x, int64_t n, float cap, sllm_stream_t stream);
+/* The seam between two sublayers, one kernel: (1) if y: x_out = x_in + post_g * y / rms(y) (x_out != x_in); (2) if has_pre:
+ * n = pre_g * x / rms(x), h = n + conv(n) with conv_w [d][taps] (last column = the current token; NULL = h = n) reaching back into
+ * the step's rows and, before a portion, into ring [slots][taps-1][d] (position p at row p % (taps-1)); h16 (or NULL) = h as dense
+ * bf16 rows; (3) the normed rows of every portion's last taps-1 tokens go to stash [T][d]; a later call with flush_ring (the ring this
+ * call read) moves them there. rms(v) = sqrt(mean(v^2) + eps). */
+int sllm_seq_seam(const sllm_seq_batch* b, const float* x_in, float* x_out, const float* y, float post_g, int32_t has_pre, float pre_g,
+                  float eps, const float* conv_w, int32_t taps, const float* ring, float* h, void* h16, float* stash, float* flush_ring,
+                  int32_t flush_taps, int32_t d, sllm_stream_t stream);
+/* out[t][c] = act(sum_j w[c][j] * x[t - taps + 1 + j][c]) (act 0 = none, 1 = silu), zeros before a sequence's start; inputs before a
+ * portion come from ring [slots][taps-1][channels] (position p at row p % (taps-1)), which is NOT updated here */
+int sllm_seq_conv_ring(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, const float* w, const float* ring,
+                       int32_t act, float* out, int32_t ldo, sllm_stream_t stream);
+/* Gated delta rule per head h over each sequence, state [slots][heads][dk][dv] fp32: S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+ * o = S^T q, with q, k (of key head h / (heads / kv_heads)) divided by sqrt(sum(x^2) + unit_eps), q times qscale,
+ * beta = sigmoid(beta_logit), g = exp(-exp(A_log[h]) * softplus(step_logit + dt_bias[h])). ring (or NULL): the last taps-1 rows of
+ * conv_x [T][channels] of every portion are stored there for the convolution of the next step. */
+int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, const float* k, int32_t ldk, const float* v, int32_t ldv,
+                        const float* beta_logit, int32_t ldb, const float* step_logit, int32_t lda, const float* A_log, const float* dt_bias,
+                        int32_t heads, int32_t kv_heads, int32_t dk, int32_t dv, float unit_eps, float qscale, float* state, float* o,
+                        int32_t ldo, const float* conv_x, int32_t ldx, int32_t channels, int32_t taps, float* ring, sllm_stream_t stream);
+/* Routing and activation of a mixture of experts, per token: s = softmax(logits[0..n_route)); the `top` largest s + correction are
+ * chosen (correction NULL = none; the lower index wins a tie); out / out16 [T][experts * ff] = act(up) * s for chosen experts with
+ * weights (the first `experts` router outputs), zeros for the others; y [T][d] = (sum of s over chosen router outputs >= experts) * h:
+ * those are experts whose output is their input. act 0 = exact gelu, 1 = tanh gelu, 2 = silu. route_w (or NULL) [T][n_route] = the
+ * weights, zero where not chosen. */
+int sllm_seq_moe_act(const float* logits, int32_t ldl, int32_t n_route, int32_t experts, int32_t top, const float* correction, const float* up,
+                     int32_t ldu, int32_t ff, int32_t act, const float* h, int32_t ldh, int32_t d, float* out, void* out16, float* y,
+                     int32_t ldy, float* route_w, int32_t T, sllm_stream_t stream);
 /* y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + bias per row (bias NULL = none); y16 (or NULL): the same rows once more, rounded
  * to bf16, dense [T][d] — the operand copy of a tensor-core product that follows */
 int sllm_seq_layernorm(const float* x, int32_t ldx, const float* w, const float* bias, float eps, float* y, int32_t ldy, void* y16,

@@ -124,8 +124,9 @@ class SeqBatch(C.Structure):
 
 
 class SeqAttnOpts(C.Structure):
-    """sllm_seq_attn_opts: window / kept first positions / score cap / distance slopes / values inside the key rows."""
-    _fields_ = [("window", _I), ("keep_first", _I), ("softcap", _F), ("slopes", _P), ("values_in_keys", _I)]
+    """sllm_seq_attn_opts: window / kept first positions / score cap / distance slopes / values inside the key rows / a charge on the
+    logarithm of the distance."""
+    _fields_ = [("window", _I), ("keep_first", _I), ("softcap", _F), ("slopes", _P), ("values_in_keys", _I), ("logdist", _P)]
 
 
 _B = C.POINTER(SeqBatch)
@@ -141,8 +142,16 @@ SIGNATURES.update({
     "sllm_seq_rotary_kv": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _F, _P, _I, _P, _P, _I, _P]),
     "sllm_seq_attention": (C.c_int, [_B, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _I, _P, C.POINTER(SeqAttnOpts), _P]),
     "sllm_seq_attention_finish": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I, _P]),
-    "sllm_seq_unit_kv": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _I, _P, _I, _I, _F, _I, _P, _I, _F, _P, _P, _I, _P]),
-    "sllm_seq_latent_kv": (C.c_int, [_B, _P, _I, _I, _I, _I, _P, _I, _I, _P, _F, _P, _I, _P, _I, _P, _I, _P]),
+    "sllm_seq_unit_kv": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _I, _P, _I, _I, _F, _I, _P, _I, _F, _P, _P, _I, _F, _I, _P]),
+    "sllm_seq_latent_kv": (C.c_int, [_B, _P, _I, _I, _I, _I, _P, _I, _I, _P, _F, _P, _I, _P, _I, _P, _I, _F, _P]),
+    "sllm_seq_embed_pair": (C.c_int, [_P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _P, _I, _P]),
+    "sllm_seq_rmsnorm_rows": (C.c_int, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
+    "sllm_seq_gated_act": (C.c_int, [_P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _P]),
+    "sllm_seq_softcap": (C.c_int, [_P, _L, _F, _P]),
+    "sllm_seq_seam": (C.c_int, [_B, _P, _P, _P, _F, _I, _F, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _P]),
+    "sllm_seq_conv_ring": (C.c_int, [_B, _P, _I, _I, _I, _P, _P, _I, _P, _I, _P]),
+    "sllm_seq_delta_rule": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _F, _F, _P, _P, _I, _P, _I, _I, _I, _P, _P]),
+    "sllm_seq_moe_act": (C.c_int, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P, _I, _P]),
     "sllm_seq_layernorm": (C.c_int, [_P, _I, _P, _P, _F, _P, _I, _P, _I, _I, _P]),
     "sllm_seq_depth_average": (C.c_int, [_P, _P, _P, _I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
     "sllm_seq_clamped_glu": (C.c_int, [_P, _I, _P, _I, _F, _F, _P, _I, _P, _I, _I, _P]),
@@ -153,7 +162,7 @@ SIGNATURES.update({
 })
 
 # The ragged-token-batch part of the library can be built and loaded on its own (`make -C csrc seq` -> libsllm_b200_seq.so: the
-# sllm_seq_* kernels, the tensor-core GEMM, the page bookkeeping, the sampler): a model made of those blocks then needs nine
+# sllm_seq_* kernels, the tensor-core GEMM, the page bookkeeping, the sampler): a model made of those blocks then needs twelve
 # translation units compiled, not all of them. The full library contains the same objects and is preferred when it exists.
 SEQ_LIB_PATH = os.path.join(HERE, "lib", "libsllm_b200_seq.so")
 SEQ_SYMBOL_PREFIXES = ("sllm_seq_", "sllm_kvpages_", "sllm_sample_", "sllm_last_error", "sllm_abi_version", "sllm_tune", "sllm_device_info",

@@ -197,6 +197,8 @@ class LatentAttentionConfig:
     scale: float
     rot: RotaryConfig
     mask: WindowMask
+    q_rank: int | None = None      # queries go through a normed latent of this width (None: one query projection)
+    kv_from: int | None = None     # the layer whose cached rows this one attends over (None: its own)
 
 
 @dataclass(frozen=True)
@@ -257,7 +259,124 @@ class SopetarConfig:
                              float((c.get("norm") or {}).get("eps", 1e-6)), tuple(layers))
 
 
-CONFIG_READERS = {"Munazen": MunazenConfig.from_dict, "Sopetar": SopetarConfig.from_dict}
+@dataclass(frozen=True)
+class LogDistanceAttentionConfig:
+    """Softmax attention without rotation in which positions enter through a charge r1_h * ln(1 + r2_h * distance) on the scores, a
+    sliding window, and a query temperature 1 + coef * ln(floor((pos + 1) / every) + 1) (``q_temp_every`` 0 = none)."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    mask: WindowMask
+    q_temp_coef: float = 0.0
+    q_temp_every: int = 0
+
+
+@dataclass(frozen=True)
+class DeltaRuleConfig:
+    """Gated delta rule: ``kv_heads`` query / key heads of width ``dim`` shared by groups of the ``heads`` value heads of width ``vdim``,
+    a causal convolution of ``conv`` taps in front of q, k and v."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+
+
+@dataclass(frozen=True)
+class GatedFeedForwardConfig:
+    ff: int
+
+
+@dataclass(frozen=True)
+class ExpertsConfig:
+    """Mixture of experts: ``experts`` feed-forwards of width ``ff`` and ``identity`` experts without weights (their output is their
+    input) share one router; a token uses the ``top`` best."""
+    experts: int
+    identity: int
+    top: int
+    ff: int
+
+
+@dataclass(frozen=True)
+class VasosunLayerConfig:
+    type: str            # "attention" | "latent_attention" | "delta"
+    mixer: object        # LogDistanceAttentionConfig | LatentAttentionConfig | DeltaRuleConfig
+    mlp: object = None   # GatedFeedForwardConfig | ExpertsConfig | None
+
+
+@dataclass(frozen=True)
+class VasosunConfig:
+    """The Vasosun design: every sublayer sits between two RMS norms whose weight is one number and reads its input through a short causal
+    convolution; the embedding adds a hashed (previous token, token) table; mixers are window attention with a logarithmic distance
+    charge, latent attention (queries through a latent too, YaRN-scaled rotation, optionally over another layer's cache) and the gated
+    delta rule; feed-forwards are gated or a mixture of experts. Every size and constant that may differ comes from config.json."""
+    architecture: str
+    vocab: int
+    width: int
+    norm_eps: float
+    conv_taps: int
+    pair_buckets: int
+    pair_mul_prev: int
+    pair_mul_cur: int
+    logit_softcap: float
+    layers: tuple
+
+    @staticmethod
+    def from_dict(c: dict) -> "VasosunConfig":
+        layers = []
+        for i, l in enumerate(c["layers"]):
+            m, mlp = l["mixer"], l.get("mlp")
+            kind = l["type"]
+            if kind == "attention":
+                heads = int(m["heads"])
+                kv_heads = int(m.get("kv_heads") or heads)
+                if heads % kv_heads:
+                    raise ValueError(f"layer {i}: {heads} query heads do not divide over {kv_heads} key/value heads")
+                qt = m.get("q_temp") or {}
+                mixer = LogDistanceAttentionConfig(heads, kv_heads, int(m["dim"]), int(m["vdim"]), float(m["scale"]), WindowMask.from_dict(m.get("mask")),
+                                                   float(qt.get("coef") or 0.0), int(qt.get("every") or 0))
+            elif kind == "latent_attention":
+                rot = m["rot"]
+                src = m.get("kv_from")
+                mixer = LatentAttentionConfig(int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"]), float(m["scale"]),
+                                              RotaryConfig(int(rot["dims"]), float(rot["base"]), rot.get("scaling") or None),
+                                              WindowMask.from_dict(m.get("mask")), int(m["q_rank"]), None if src is None else int(src))
+                if mixer.rot.dims > mixer.rot_dim or mixer.rot.dims % 2:
+                    raise ValueError(f"layer {i}: {mixer.rot.dims} rotary dimensions do not fit a rotated part of {mixer.rot_dim}")
+                if mixer.kv_from is not None:
+                    o = layers[mixer.kv_from].mixer if 0 <= mixer.kv_from < i and layers[mixer.kv_from].type == kind else None
+                    if o is None or o.kv_from is not None or (o.kv_rank, o.rot_dim, o.rot) != (mixer.kv_rank, mixer.rot_dim, mixer.rot):
+                        raise ValueError(f"layer {i}: kv_from {mixer.kv_from} must name an earlier latent-attention layer with a cache of its own "
+                                         "and the same latent width and rotation")
+            elif kind == "delta":
+                heads = int(m["heads"])
+                kv_heads = int(m.get("kv_heads") or heads)
+                if heads % kv_heads:
+                    raise ValueError(f"layer {i}: {heads} value heads do not divide over {kv_heads} key heads")
+                mixer = DeltaRuleConfig(heads, kv_heads, int(m["dim"]), int(m["vdim"]), int(m.get("conv") or 1))
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            ff = None
+            if mlp is not None:
+                if mlp.get("kind", "dense") == "dense":
+                    ff = GatedFeedForwardConfig(int(mlp["ff"]))
+                elif mlp["kind"] == "moe":
+                    r = mlp["router"]
+                    ff = ExpertsConfig(int(r["experts"]), int(r.get("identity") or 0), int(r["top"]), int(mlp["expert"]["ff"]))
+                    if not 1 <= ff.top <= ff.experts + ff.identity:
+                        raise ValueError(f"layer {i}: {ff.top} of {ff.experts + ff.identity} experts")
+                else:
+                    raise ValueError(f"layer {i}: feed-forward kind {mlp['kind']!r} is not part of this design")
+            layers.append(VasosunLayerConfig(kind, mixer, ff))
+        pair = (c.get("embedding") or {}).get("bigram") or {}
+        return VasosunConfig(c["architecture"], int(c["vocab"]), int(c["width"]), float((c.get("norm") or {}).get("eps", 1e-6)),
+                             int((c.get("canon") or {}).get("taps") or 1), int(pair.get("buckets") or 0), int(pair.get("mul_prev") or 0),
+                             int(pair.get("mul_cur") or 0), float(c.get("logit_softcap") or 0.0), tuple(layers))
+
+
+CONFIG_READERS = {"Munazen": MunazenConfig.from_dict, "Sopetar": SopetarConfig.from_dict, "Vasosun": VasosunConfig.from_dict}
 
 
 def read_model_config(model_dir: str):

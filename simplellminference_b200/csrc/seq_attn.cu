@@ -32,6 +32,7 @@ struct AttnArgs {
     float softcap;            // > 0: score <- softcap * tanh(score / softcap)
     const float* slopes;      // [heads] or NULL: score <- score - slopes[h] * (i - j)
     int v_in_k;               // values = the first dv columns of the key rows (v_pool unused)
+    const float* logdist;     // [2][heads] or NULL: score <- score - r1[h] * ln(1 + r2[h] * (i - j)), r1 = row 0, r2 = row 1
 };
 
 // The key tiles a CTA whose queries lie at positions first .. last has to visit: the tiles of the kept first positions, then the tiles
@@ -48,10 +49,12 @@ struct TileList {
     __device__ __forceinline__ int tile_of(int idx) const { return idx < n_keep ? idx : lo + idx - n_keep; }
 };
 
-__device__ __forceinline__ float seq_score(float dot, float scale, float softcap, float slope, int qpos, int key) {
+__device__ __forceinline__ float seq_score(float dot, float scale, float softcap, float slope, float r1, float r2, int qpos, int key) {
     float sc = dot * scale;
     if (softcap > 0.0f) sc = softcap * tanhf(sc / softcap);
-    return sc - slope * (float)(qpos - key);
+    sc -= slope * (float)(qpos - key);
+    if (r1 != 0.0f) sc -= r1 * log1pf(r2 * (float)(qpos - key));
+    return sc;
 }
 __device__ __forceinline__ bool seq_sees(int qpos, int key, int window, int keep_first) {
     return key <= qpos && (qpos - key < window || key < keep_first);
@@ -95,6 +98,13 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
     float slope[kQW];
 #pragma unroll
     for (int i = 0; i < kQW; ++i) slope[i] = (p.slopes && warp * kQW + i < nq) ? p.slopes[row_head(warp * kQW + i)] : 0.0f;
+    float r1[kQW], r2[kQW];
+#pragma unroll
+    for (int i = 0; i < kQW; ++i) {
+        const bool has = p.logdist && warp * kQW + i < nq;
+        r1[i] = has ? p.logdist[row_head(warp * kQW + i)] : 0.0f;
+        r2[i] = has ? p.logdist[p.heads + row_head(warp * kQW + i)] : 0.0f;
+    }
     const int last_pos = row_pos(nq - 1);
     const TileList tiles(row_pos(0), last_pos, p.window, p.keep_first, kBK);
     for (int idx = split; idx < tiles.n; idx += p.nsplit) {
@@ -152,7 +162,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
         for (int i = 0; i < kQW; ++i) {
             const int qi = warp * kQW + i;
             const bool see = qi < nq && seq_sees(row_pos(qi), j0 + lane, p.window, p.keep_first);
-            const float sc = see ? seq_score(s[i], p.scale, p.softcap, slope[i], row_pos(qi), j0 + lane) : -INFINITY;
+            const float sc = see ? seq_score(s[i], p.scale, p.softcap, slope[i], r1[i], r2[i], row_pos(qi), j0 + lane) : -INFINITY;
             const float mn = fmaxf(m[i], warp_max(sc));
             const float corr = (mn == -INFINITY) ? 1.0f : expf(m[i] - mn);   // m = -inf: nothing accumulated yet, expf(-inf) = 0 is right too
             pw[i] = see ? expf(sc - mn) : 0.0f;
@@ -248,6 +258,7 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
     const int last_pos = pos0 + nq - 1;
     const TileList tiles(pos0, last_pos, p.window, p.keep_first, kBK);
     const float slope = p.slopes ? p.slopes[h] : 0.0f;
+    const float ld1 = p.logdist ? p.logdist[h] : 0.0f, ld2 = p.logdist ? p.logdist[p.heads + h] : 0.0f;
 
     // tile kt of the sequence -> stage `st` of shared memory, asynchronously (rows beyond the last position are zero-filled)
     auto issue = [&](int kt, int st) {
@@ -324,7 +335,7 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
                 const int key = j0 + nt * 8 + 2 * c + (e & 1);
                 const int qpos = pos0 + ((e < 2) ? r0 : r1);
                 const bool see = ((e < 2) ? ok0 : ok1) && seq_sees(qpos, key, p.window, p.keep_first);
-                s[nt][e] = see ? seq_score(s[nt][e], p.scale, p.softcap, slope, qpos, key) : -INFINITY;
+                s[nt][e] = see ? seq_score(s[nt][e], p.scale, p.softcap, slope, ld1, ld2, qpos, key) : -INFINITY;
             }
             mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
             mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
@@ -566,13 +577,14 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
     const int dkp = ((dk + 3) & ~3) + 4;
     const size_t smem = ((size_t)(kBQ + kBK) * dkp + (v_in_k ? 0 : (size_t)kBK * dv)) * sizeof(float);
     SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes(), SLLM_ENOTSUP, "seq_attention: heads of %d + %d floats need %zu bytes of shared memory", dk, dv, smem);
-    AttnArgs p{*b, q, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws, 0, INT_MAX, 0, 0.0f, nullptr, 0};
+    AttnArgs p{*b, q, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws, 0, INT_MAX, 0, 0.0f, nullptr, 0, nullptr};
     if (opts) {
         p.window = opts->window > 0 ? opts->window : INT_MAX;
         p.keep_first = opts->window > 0 ? opts->keep_first : 0;
         p.softcap = opts->softcap;
         p.slopes = opts->slopes;
         p.v_in_k = v_in_k;
+        p.logdist = opts->logdist;
     }
     dim3 grid(b->n_qtiles, heads, nsplit);
     // steps that hold a portion of a prompt, bf16 pools, head widths the fragments take: the tensor-core body

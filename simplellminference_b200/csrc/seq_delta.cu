@@ -1,0 +1,185 @@
+// csrc/seq_delta.cu — the gated delta rule over the ragged token batch, and the short causal convolution (with an activation) in front
+// of it. Per head the state S [dk][dv] (fp32, one per sequence slot) follows
+//     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+// with q and k made unit vectors per head (q also times dk^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) * softplus(a + dt_bias)).
+// Everything that enters the recurrence is fp32. The columns of S are independent recurrences that share k, q, beta and g: a thread
+// owns a piece (32 key channels) of one column in registers; the pieces of a column sit in adjacent lanes and meet by shuffles.
+//
+// The convolution keeps its last taps-1 inputs per sequence in a ring (position p at row p % (taps-1)); the recurrence kernel, which
+// runs after the convolution has read the ring, stores the portion's last inputs there.
+#include "seq_common.cuh"
+
+namespace sllm {
+
+// thread = (token, channel): out = act(sum_j w[c][j] * x[t - taps + 1 + j][c]); act 0 = none, 1 = silu
+__global__ void seq_conv_ring_kernel(sllm_seq_batch b, const float* __restrict__ x, int ldx, int channels, int taps, const float* __restrict__ w,
+                                     const float* __restrict__ ring, int act, float* __restrict__ out, int ldo) {
+    const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int slot = b.tok_slot[t], pos = b.tok_pos[t];
+    float acc = w[(size_t)c * taps + taps - 1] * x[(size_t)t * ldx + c];
+    for (int back = 1; back < taps; ++back) {
+        if (pos - back < 0) break;
+        const float xv = (t - back >= 0 && b.tok_slot[t - back] == slot) ? x[(size_t)(t - back) * ldx + c]
+                                                                          : ring[((size_t)slot * (taps - 1) + (pos - back) % (taps - 1)) * channels + c];
+        acc = fmaf(w[(size_t)c * taps + taps - 1 - back], xv, acc);
+    }
+    if (act == 1) acc = acc * seq_sigmoid(acc);
+    out[(size_t)t * ldo + c] = acc;
+}
+
+struct DeltaArgs {
+    sllm_seq_batch b;
+    const float *q, *k, *v; int ldq, ldk, ldv;          // after convolution and activation; q / k [kv_heads][dk], v [heads][dv] per token
+    const float *bl, *al; int ldb, lda;                 // logits of beta and of the decay's step, [heads] per token
+    const float *A_log, *dt_bias;                       // [heads]
+    int heads, kv_heads, dk, dv;
+    float unit_eps, qscale;
+    float* state;                                       // [slots][heads][dk][dv]
+    float* o; int ldo;                                  // [T][heads * dv]
+    const float* conv_x; int ldx, channels, taps; float* ring;   // inputs of the convolution, stored to the ring for the next step (NULL = not)
+    int chunk, PP;
+};
+
+constexpr int kDeltaKP = 32;      // key channels of a thread
+constexpr int kDeltaRS = kDeltaKP + 1;   // a piece's stride in shared memory (pieces of the same index then lie in different banks)
+
+// CTA = (segment, head); thread = (value column j, piece `part` of the key channels), part = tid % PP
+__global__ void __launch_bounds__(1024) seq_delta_kernel(DeltaArgs p) {
+    extern __shared__ float dsm[];
+    const sllm_seq_batch& b = p.b;
+    const int seg = blockIdx.x, h = blockIdx.y, kvh = h / (p.heads / p.kv_heads);
+    const int start = b.seg_start[seg], len = b.seg_len[seg], slot = b.seg_slot[seg], pos0 = b.seg_pos0[seg];
+    const int dk = p.dk, dv = p.dv, PP = p.PP, C = p.chunk, RS = PP * kDeltaRS;
+    const int part = threadIdx.x % PP, j = threadIdx.x / PP;
+    const bool live = j < dv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    float* s_k = dsm;                 // [C][RS]
+    float* s_q = s_k + C * RS;        // [C][RS]
+    float* s_v = s_q + C * RS;        // [C][dv]
+    float* s_o = s_v + C * dv;        // [C][dv]
+    float* s_beta = s_o + C * dv;     // [C]
+    float* s_g = s_beta + C;          // [C]
+    float* st = p.state + ((size_t)slot * p.heads + h) * dk * dv;
+    float S[kDeltaKP];
+#pragma unroll
+    for (int x = 0; x < kDeltaKP; ++x) {
+        const int kr = part * kDeltaKP + x;
+        S[x] = (live && kr < dk) ? st[(size_t)kr * dv + j] : 0.0f;
+    }
+    const float rate = expf(p.A_log[h]), bias = p.dt_bias[h];
+    for (int c0 = 0; c0 < len; c0 += C) {
+        const int n = min(C, len - c0);
+        for (int i = threadIdx.x; i < n * PP * kDeltaKP; i += blockDim.x) {        // channels beyond dk are zeros
+            const int tok = i / (PP * kDeltaKP), kr = i % (PP * kDeltaKP);
+            const size_t t = (size_t)(start + c0 + tok);
+            const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + kr % kDeltaKP;
+            s_k[at] = kr < dk ? p.k[t * p.ldk + (size_t)kvh * dk + kr] : 0.0f;
+            s_q[at] = kr < dk ? p.q[t * p.ldq + (size_t)kvh * dk + kr] : 0.0f;
+        }
+        for (int i = threadIdx.x; i < n * dv; i += blockDim.x) s_v[i] = p.v[(size_t)(start + c0 + i / dv) * p.ldv + (size_t)h * dv + i % dv];
+        if (threadIdx.x < n) {
+            const size_t t = (size_t)(start + c0 + threadIdx.x);
+            s_beta[threadIdx.x] = seq_sigmoid(p.bl[t * p.ldb + h]);
+            s_g[threadIdx.x] = expf(-rate * seq_softplus(p.al[t * p.lda + h] + bias));
+        }
+        __syncthreads();
+        for (int tok = warp; tok < n; tok += nwarps) {                             // unit vectors: a warp per token
+            float sk = 0.0f, sq = 0.0f;
+            for (int kr = lane; kr < PP * kDeltaKP; kr += 32) {                    // lane = offset in a piece, one piece per round
+                const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + lane;
+                sk = fmaf(s_k[at], s_k[at], sk);
+                sq = fmaf(s_q[at], s_q[at], sq);
+            }
+            const float ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps), iq = p.qscale / sqrtf(warp_sum(sq) + p.unit_eps);
+            for (int kr = lane; kr < PP * kDeltaKP; kr += 32) {
+                const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + lane;
+                s_k[at] *= ik;
+                s_q[at] *= iq;
+            }
+        }
+        __syncthreads();
+        for (int i = 0; i < n; ++i) {
+            const float g = s_g[i], beta = s_beta[i];
+            const float* kk = s_k + i * RS + part * kDeltaRS;
+            const float* qq = s_q + i * RS + part * kDeltaRS;
+            float dot = 0.0f;
+#pragma unroll
+            for (int x = 0; x < kDeltaKP; ++x) {
+                S[x] *= g;
+                dot = fmaf(S[x], kk[x], dot);
+            }
+            for (int o = PP >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            const float u = beta * ((live ? s_v[i * dv + j] : 0.0f) - dot);
+            float out = 0.0f;
+#pragma unroll
+            for (int x = 0; x < kDeltaKP; ++x) {
+                S[x] = fmaf(kk[x], u, S[x]);
+                out = fmaf(S[x], qq[x], out);
+            }
+            for (int o = PP >> 1; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+            if (live && part == 0) s_o[i * dv + j] = out;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < n * dv; i += blockDim.x) p.o[(size_t)(start + c0 + i / dv) * p.ldo + (size_t)h * dv + i % dv] = s_o[i];
+        __syncthreads();
+    }
+    if (live) {
+#pragma unroll
+        for (int x = 0; x < kDeltaKP; ++x) {
+            const int kr = part * kDeltaKP + x;
+            if (kr < dk) st[(size_t)kr * dv + j] = S[x];
+        }
+    }
+    if (p.ring && p.taps > 1) {          // the heads of a segment share the job of storing its last inputs of the convolution
+        const int keep = min(len, p.taps - 1);
+        for (int i = h * blockDim.x + threadIdx.x; i < keep * p.channels; i += p.heads * blockDim.x) {
+            const int r = len - keep + i / p.channels, c = i % p.channels;
+            p.ring[((size_t)slot * (p.taps - 1) + (pos0 + r) % (p.taps - 1)) * p.channels + c] = p.conv_x[(size_t)(start + r) * p.ldx + c];
+        }
+    }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+extern "C" {
+
+int sllm_seq_conv_ring(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, const float* w, const float* ring, int32_t act,
+                       float* out, int32_t ldo, sllm_stream_t stream) {
+    SLLM_REQUIRE(b && b->T > 0 && b->tok_slot && b->tok_pos, SLLM_EINVAL, "seq_conv_ring: incomplete batch description");
+    SLLM_REQUIRE(x && w && out && channels > 0 && taps >= 1 && (taps == 1 || ring) && (act == 0 || act == 1), SLLM_EINVAL, "seq_conv_ring: bad argument");
+    SLLM_REQUIRE(b->T <= 65535, SLLM_ENOTSUP, "seq_conv_ring: at most 65535 tokens per step");
+    seq_conv_ring_kernel<<<dim3((channels + 127) / 128, b->T), 128, 0, as_stream(stream)>>>(*b, x, ldx, channels, taps, w, ring, act, out, ldo);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, const float* k, int32_t ldk, const float* v, int32_t ldv, const float* beta_logit,
+                        int32_t ldb, const float* step_logit, int32_t lda, const float* A_log, const float* dt_bias, int32_t heads, int32_t kv_heads,
+                        int32_t dk, int32_t dv, float unit_eps, float qscale, float* state, float* o, int32_t ldo, const float* conv_x, int32_t ldx,
+                        int32_t channels, int32_t taps, float* ring, sllm_stream_t stream) {
+    SLLM_REQUIRE(b && b->T > 0 && b->nseg > 0 && b->seg_start && b->seg_len && b->seg_slot && b->seg_pos0, SLLM_EINVAL, "seq_delta_rule: incomplete batch description");
+    SLLM_REQUIRE(q && k && v && beta_logit && step_logit && A_log && dt_bias && state && o, SLLM_EINVAL, "seq_delta_rule: bad argument");
+    SLLM_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0, SLLM_EINVAL, "seq_delta_rule: %d heads over %d key heads", heads, kv_heads);
+    SLLM_REQUIRE(!ring || (conv_x && channels > 0 && taps >= 1), SLLM_EINVAL, "seq_delta_rule: the ring needs the convolution's inputs");
+    const int parts = (dk + kDeltaKP - 1) / kDeltaKP;
+    int PP = 1;
+    while (PP < parts) PP *= 2;
+    SLLM_REQUIRE(PP <= 32 && (long long)dv * PP <= 1024, SLLM_ENOTSUP, "seq_delta_rule: a %d x %d state does not fit one thread block (dk/32 * dv <= 1024)", dk, dv);
+    const int threads = (dv * PP + 31) / 32 * 32;
+    const int per_tok = 2 * PP * kDeltaRS + 2 * dv + 2;
+    const int chunk = std::max(1, std::min(16, 10240 / per_tok));
+    const size_t smem = (size_t)chunk * per_tok * sizeof(float);
+    SLLM_REQUIRE(smem <= 48 * 1024, SLLM_ENOTSUP, "seq_delta_rule: one token of a %d x %d head needs %zu bytes of shared memory", dk, dv, smem);
+    DeltaArgs p{*b, q, k, v, ldq, ldk, ldv, beta_logit, step_logit, ldb, lda, A_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale, state, o, ldo,
+                conv_x, ldx, channels, taps, ring, chunk, PP};
+    seq_delta_kernel<<<dim3(b->nseg, heads), threads, smem, as_stream(stream)>>>(p);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+}  // extern "C"

@@ -255,6 +255,49 @@ __global__ void seq_clamped_glu_kernel(const float* __restrict__ gate, int ldg, 
     }
 }
 
+// token embedding plus a hashed embedding of the (previous token, token) pair: row (prev * mul_prev + id * mul_cur) mod buckets of
+// `pairs`, and row `buckets` (the table's last) for a sequence's first token (prev < 0)
+__global__ void seq_embed_pair_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ prev, const void* __restrict__ table,
+                                      const void* __restrict__ pairs, int w_dtype, int vocab, int d, int buckets, long long mul_prev, long long mul_cur,
+                                      float* __restrict__ out) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const int pv = prev[t];
+    const long long row = pv < 0 ? (long long)buckets : (((long long)pv * mul_prev + (long long)id * mul_cur) % buckets + buckets) % buckets;
+    for (int j = threadIdx.x; j < d; j += blockDim.x)
+        out[(size_t)t * d + j] = seq_ldw(table, w_dtype, (size_t)id * d + j) + seq_ldw(pairs, w_dtype, (size_t)row * d + j);
+}
+
+// one warp per row: y = x / sqrt(mean(x^2) + eps) * w (w NULL = no weight)
+__global__ void seq_rmsnorm_rows_kernel(const float* x, int ldx, const float* __restrict__ w, float eps, float* y, int ldy, int T, int n) {   // y may be x
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const float* xr = x + (size_t)t * ldx;
+    float ss = 0.0f;
+    for (int j = lane; j < n; j += 32) ss = fmaf(xr[j], xr[j], ss);
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + eps);
+    for (int j = lane; j < n; j += 32) y[(size_t)t * ldy + j] = (xr[j] * inv) * (w ? w[j] : 1.0f);
+}
+
+// out = act(gate) * up; act 0 = silu
+__global__ void seq_gated_act_kernel(const float* __restrict__ gate, int ldg, const float* __restrict__ up, int ldu, int act, float* __restrict__ out,
+                                     int ldo, uint16_t* __restrict__ out16, int T, int n) {
+    const size_t total = (size_t)T * n;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / n, j = i % n;
+        const float g = gate[t * ldg + j];
+        const float v = (g * seq_sigmoid(g)) * up[t * ldu + j];
+        if (out) out[t * ldo + j] = v;
+        if (out16) out16[i] = f32_to_bf16_bits(v);
+    }
+}
+
+// x <- cap * tanh(x / cap)
+__global__ void seq_softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] = cap * tanhf(x[i] / cap);
+}
+
 // Threads of a one-CTA-per-row kernel: steps of few tokens have few CTAs, and a row walked by 128 threads is a chain of dependent
 // memory latencies (32 of them at 4096 floats); with up to 1024 threads every thread touches the row once or twice.
 static int row_threads(int T, int items, int many_rows_threads) {
@@ -375,6 +418,44 @@ int sllm_seq_clamped_glu(const float* gate, int32_t ldg, const float* up, int32_
     const size_t total = (size_t)T * n;
     seq_clamped_glu_kernel<<<(int)std::min<size_t>((total + 255) / 256, (size_t)sm_count() * 8), 256, 0, as_stream(stream)>>>(gate, ldg, up, ldu, limit, alpha, out,
                                                                                                                        ldo, (uint16_t*)out16, T, n);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_embed_pair(const int32_t* ids, const int32_t* prev_ids, const void* table, const void* pairs, int32_t w_dtype, int32_t vocab, int32_t d,
+                        int32_t buckets, int64_t mul_prev, int64_t mul_cur, float* out, int32_t T, sllm_stream_t stream) {
+    SLLM_REQUIRE(ids && prev_ids && table && pairs && out && T > 0 && d > 0 && vocab > 0 && buckets > 0, SLLM_EINVAL, "seq_embed_pair: bad argument");
+    SLLM_REQUIRE(w_dtype == SLLM_F32 || w_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_embed_pair: fp32 or bf16 tables");
+    seq_embed_pair_kernel<<<T, row_threads(T, d, 128), 0, as_stream(stream)>>>(ids, prev_ids, table, pairs, w_dtype, vocab, d, buckets, mul_prev, mul_cur, out);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_rmsnorm_rows(const float* x, int32_t ldx, const float* w, float eps, float* y, int32_t ldy, int32_t T, int32_t n, sllm_stream_t stream) {
+    SLLM_REQUIRE(x && y && T > 0 && n > 0 && ldx >= n && ldy >= n, SLLM_EINVAL, "seq_rmsnorm_rows: bad argument");
+    seq_rmsnorm_rows_kernel<<<(T + 3) / 4, 128, 0, as_stream(stream)>>>(x, ldx, w, eps, y, ldy, T, n);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_gated_act(const float* gate, int32_t ldg, const float* up, int32_t ldu, int32_t act, float* out, int32_t ldo, void* out16, int32_t T, int32_t n,
+                       sllm_stream_t stream) {
+    SLLM_REQUIRE(gate && up && (out || out16) && T > 0 && n > 0 && ldg >= n && ldu >= n && (!out || ldo >= n), SLLM_EINVAL, "seq_gated_act: bad argument");
+    SLLM_REQUIRE(act == 0, SLLM_ENOTSUP, "seq_gated_act: activation 0 (silu)");
+    const size_t total = (size_t)T * n;
+    seq_gated_act_kernel<<<(int)std::min<size_t>((total + 255) / 256, (size_t)sm_count() * 8), 256, 0, as_stream(stream)>>>(gate, ldg, up, ldu, act, out, ldo,
+                                                                                                                     (uint16_t*)out16, T, n);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_softcap(float* x, int64_t n, float cap, sllm_stream_t stream) {
+    SLLM_REQUIRE(x && n > 0 && cap > 0.0f, SLLM_EINVAL, "seq_softcap: bad argument");
+    seq_softcap_kernel<<<(int)std::min<size_t>(((size_t)n + 255) / 256, (size_t)sm_count() * 8), 256, 0, as_stream(stream)>>>(x, (size_t)n, cap);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

@@ -12,17 +12,22 @@ namespace sllm {
 template <typename KV>
 __global__ void seq_unit_kv_kernel(sllm_seq_batch b, float* __restrict__ q, int ldq, int heads, int dk, const float* __restrict__ k, int ldk, int kv_heads,
                                    const float* __restrict__ v, int ldv, int dv, float eps, int unit, float* __restrict__ v_shared, int share, float lambda,
-                                   KV* __restrict__ k_pool, KV* __restrict__ v_pool) {
+                                   float q_temp_coef, int q_temp_every, KV* __restrict__ k_pool, KV* __restrict__ v_pool) {
     const int t = blockIdx.x, item = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (item >= heads + 2 * kv_heads) return;
     const int pos = b.tok_pos[t], slot = b.tok_slot[t];
     const int page = b.block_table[(size_t)slot * b.max_pages + pos / b.page_len], in_page = pos % b.page_len;
     if (item < heads) {                                  // a query head, in place
-        if (!(unit & 1)) return;
+        // query temperature: queries grow with the logarithm of the position, in steps of q_temp_every positions
+        const float temp = q_temp_every > 0 ? 1.0f + q_temp_coef * logf((float)((pos + 1) / q_temp_every) + 1.0f) : 1.0f;
+        if (!(unit & 1) && temp == 1.0f) return;
         float* row = q + (size_t)t * ldq + (size_t)item * dk;
-        float ss = 0.0f;
-        for (int j = lane; j < dk; j += 32) ss = fmaf(row[j], row[j], ss);
-        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps);
+        float inv = temp;
+        if (unit & 1) {
+            float ss = 0.0f;
+            for (int j = lane; j < dk; j += 32) ss = fmaf(row[j], row[j], ss);
+            inv = temp / sqrtf(warp_sum(ss) / (float)dk + eps);
+        }
         for (int j = lane; j < dk; j += 32) row[j] *= inv;
     } else if (item < heads + kv_heads) {                // a key head -> pool
         const int g = item - heads;
@@ -58,23 +63,28 @@ __global__ void seq_unit_kv_kernel(sllm_seq_batch b, float* __restrict__ q, int 
 // one CTA per token
 template <typename KV>
 __global__ void seq_latent_kv_kernel(sllm_seq_batch b, const float* __restrict__ q, int ldq, int heads, int dn, int dr, const float* __restrict__ low, int ldlow,
-                                     int rank, const float* __restrict__ norm_w, float eps, const double* __restrict__ freq, int n_freq,
+                                     int rank, const float* __restrict__ norm_w, float eps, const double* __restrict__ freq, int n_freq, float magnitude,
                                      float* __restrict__ q_out, int ldqo, KV* __restrict__ pool) {
     __shared__ float red[33];
     const int t = blockIdx.x, pos = b.tok_pos[t], slot = b.tok_slot[t];
     const int page = b.block_table[(size_t)slot * b.max_pages + pos / b.page_len], in_page = pos % b.page_len;
-    const float* lr = low + (size_t)t * ldlow;
+    const float* lr = low ? low + (size_t)t * ldlow : nullptr;   // no low-rank row: the layer reads another layer's cache, only its queries turn
     const size_t dst = seq_pool_row(page, 1, 0, b.page_len, in_page, rank + dr);
-    float ss = 0.0f;
-    for (int j = threadIdx.x; j < rank; j += blockDim.x) ss = fmaf(lr[j], lr[j], ss);
-    ss = block_sum(ss, red);
-    const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
-    for (int j = threadIdx.x; j < rank; j += blockDim.x) seq_st(pool, dst + j, (lr[j] * inv) * norm_w[j]);
+    const int items = low ? heads + 1 : heads;
+    if (low) {
+        float ss = 0.0f;
+        for (int j = threadIdx.x; j < rank; j += blockDim.x) ss = fmaf(lr[j], lr[j], ss);
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+        for (int j = threadIdx.x; j < rank; j += blockDim.x) seq_st(pool, dst + j, (lr[j] * inv) * norm_w[j]);
+    }
     // rotated pairs: item 0 .. heads-1 = the query heads, item heads = the shared key part; the first 2 * n_freq dimensions turn
-    for (int i = threadIdx.x; i < (heads + 1) * n_freq; i += blockDim.x) {
+    for (int i = threadIdx.x; i < items * n_freq; i += blockDim.x) {
         const int h = i / n_freq, mi = i % n_freq;
         float sn, cs;
         seq_angle(pos, freq[mi], &sn, &cs);
+        sn *= magnitude;
+        cs *= magnitude;
         const float* src = h < heads ? q + (size_t)t * ldq + (size_t)h * (dn + dr) + dn : lr + rank;
         const float u = src[2 * mi], w = src[2 * mi + 1];
         const float a = u * cs - w * sn, c = w * cs + u * sn;
@@ -88,7 +98,7 @@ __global__ void seq_latent_kv_kernel(sllm_seq_batch b, const float* __restrict__
         }
     }
     const int rest = dr - 2 * n_freq;                     // dimensions of the rotated part beyond the rotary ones pass unchanged
-    for (int i = threadIdx.x; i < (heads + 1) * rest; i += blockDim.x) {
+    for (int i = threadIdx.x; i < items * rest; i += blockDim.x) {
         const int h = i / rest, j = 2 * n_freq + i % rest;
         if (h < heads) q_out[(size_t)t * ldqo + (size_t)h * (rank + dr) + rank + j] = q[(size_t)t * ldq + (size_t)h * (dn + dr) + dn + j];
         else seq_st(pool, dst + rank + j, lr[rank + j]);
@@ -103,7 +113,7 @@ extern "C" {
 
 int sllm_seq_unit_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t heads, int32_t dk, const float* k, int32_t ldk, int32_t kv_heads,
                      const float* v, int32_t ldv, int32_t dv, float eps, int32_t unit, float* v_shared, int32_t share, float lambda, void* k_pool,
-                     void* v_pool, int32_t kv_dtype, sllm_stream_t stream) {
+                     void* v_pool, int32_t kv_dtype, float q_temp_coef, int32_t q_temp_every, sllm_stream_t stream) {
     SLLM_REQUIRE(b && b->T > 0 && b->tok_slot && b->tok_pos && b->block_table, SLLM_EINVAL, "seq_unit_kv: incomplete batch description");
     SLLM_REQUIRE(q && k && v && k_pool && v_pool && heads > 0 && kv_heads > 0 && dk > 0 && dv > 0, SLLM_EINVAL, "seq_unit_kv: bad argument");
     SLLM_REQUIRE(share >= 0 && share <= 2 && (share == 0 || v_shared), SLLM_EINVAL, "seq_unit_kv: share 0 (none), 1 (write) or 2 (blend) with a buffer");
@@ -111,10 +121,10 @@ int sllm_seq_unit_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t hea
     const dim3 grid(b->T, (heads + 2 * kv_heads + 3) / 4);
     if (kv_dtype == SLLM_F32)
         seq_unit_kv_kernel<float><<<grid, 128, 0, as_stream(stream)>>>(*b, q, ldq, heads, dk, k, ldk, kv_heads, v, ldv, dv, eps, unit, v_shared, share, lambda,
-                                                                       (float*)k_pool, (float*)v_pool);
+                                                                       q_temp_coef, q_temp_every, (float*)k_pool, (float*)v_pool);
     else
         seq_unit_kv_kernel<uint16_t><<<grid, 128, 0, as_stream(stream)>>>(*b, q, ldq, heads, dk, k, ldk, kv_heads, v, ldv, dv, eps, unit, v_shared, share, lambda,
-                                                                          (uint16_t*)k_pool, (uint16_t*)v_pool);
+                                                                          q_temp_coef, q_temp_every, (uint16_t*)k_pool, (uint16_t*)v_pool);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
@@ -122,17 +132,17 @@ int sllm_seq_unit_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t hea
 
 int sllm_seq_latent_kv(const sllm_seq_batch* b, const float* q, int32_t ldq, int32_t heads, int32_t dn, int32_t dr, const float* low, int32_t ldlow,
                        int32_t rank, const float* norm_w, float eps, const double* freq, int32_t n_freq, float* q_out, int32_t ldqo, void* pool,
-                       int32_t kv_dtype, sllm_stream_t stream) {
+                       int32_t kv_dtype, float magnitude, sllm_stream_t stream) {
     SLLM_REQUIRE(b && b->T > 0 && b->tok_slot && b->tok_pos && b->block_table, SLLM_EINVAL, "seq_latent_kv: incomplete batch description");
-    SLLM_REQUIRE(q && low && norm_w && q_out && pool && heads > 0 && dn >= 0 && dr >= 0 && rank > 0, SLLM_EINVAL, "seq_latent_kv: bad argument");
+    SLLM_REQUIRE(q && q_out && (!low || (norm_w && pool)) && heads > 0 && dn >= 0 && dr >= 0 && rank > 0, SLLM_EINVAL, "seq_latent_kv: bad argument");
     SLLM_REQUIRE(n_freq >= 0 && 2 * n_freq <= dr && (n_freq == 0 || freq), SLLM_EINVAL, "seq_latent_kv: %d rotary pairs do not fit %d dimensions", n_freq, dr);
     SLLM_REQUIRE(kv_dtype == SLLM_F32 || kv_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_latent_kv: fp32 or bf16 pools");
     const int threads = rank >= 512 ? 256 : 128;
     if (kv_dtype == SLLM_F32)
-        seq_latent_kv_kernel<float><<<b->T, threads, 0, as_stream(stream)>>>(*b, q, ldq, heads, dn, dr, low, ldlow, rank, norm_w, eps, freq, n_freq, q_out, ldqo,
+        seq_latent_kv_kernel<float><<<b->T, threads, 0, as_stream(stream)>>>(*b, q, ldq, heads, dn, dr, low, ldlow, rank, norm_w, eps, freq, n_freq, magnitude, q_out, ldqo,
                                                                              (float*)pool);
     else
-        seq_latent_kv_kernel<uint16_t><<<b->T, threads, 0, as_stream(stream)>>>(*b, q, ldq, heads, dn, dr, low, ldlow, rank, norm_w, eps, freq, n_freq, q_out,
+        seq_latent_kv_kernel<uint16_t><<<b->T, threads, 0, as_stream(stream)>>>(*b, q, ldq, heads, dn, dr, low, ldlow, rank, norm_w, eps, freq, n_freq, magnitude, q_out,
                                                                                 ldqo, (uint16_t*)pool);
     ++g_launches;
     SLLM_LAUNCH_CHECK();

@@ -1,0 +1,124 @@
+// csrc/seq_sublayer.cu — the seam between two sublayers of a model whose sublayers are wrapped in scalar RMS norms and read their input
+// through a short causal convolution: x <- x + g_post * y / rms(y) (the residual sum, fp32), then h = n + conv(n) with
+// n = g_pre * x / rms(x) and conv a per-channel causal convolution over time, as ONE kernel. A norm here has one number as its weight.
+//
+// The convolution reaches taps-1 tokens back. Inside a portion those are rows of this step: a CTA (one per token) recomputes the
+// residual sum and the norm of its predecessors from the sublayer's input and output (x is therefore read from one buffer and written to
+// another). Before the portion they come from the sequence's state: a ring of taps-1 normed rows per slot, position p at row
+// p % (taps-1). A ring may not be written while other CTAs of the launch still read it, so the normed rows of a portion's last tokens
+// go to a per-token stash, and the NEXT seam launch moves them into the ring (`flush_*`); the model's last seam (the final norm, no
+// convolution) flushes the last ring.
+#include "seq_common.cuh"
+
+namespace sllm {
+
+struct SeamArgs {
+    sllm_seq_batch b;
+    const float* x_in; float* x_out;          // residual stream before / after the sum (x_out unused when y is NULL)
+    const float* y; float post_g;             // sublayer output and its norm's weight; NULL = no sum
+    int has_pre; float pre_g, eps;            // 0 = only the sum
+    const float* conv_w; int taps;            // [d][taps], last column = the current token; NULL = no convolution
+    const float* ring;                        // [slots][taps-1][d]
+    float* h; uint16_t* h16;                  // what the next sublayer reads, fp32 and (optionally) as bf16 operand rows
+    float* stash;                             // [T][d]: normed rows of tokens that a later launch moves into `ring`
+    float* flush_ring; int flush_taps;        // the ring that takes the stash the previous seam left
+    int d;
+};
+
+// is token t among the last `keep` tokens of its portion?
+__device__ __forceinline__ bool seam_is_last(const sllm_seq_batch& b, int t, int slot, int keep) {
+    return keep > 0 && (t + keep >= b.T || b.tok_slot[t + keep] != slot);
+}
+
+__global__ void seq_seam_kernel(SeamArgs p) {
+    extern __shared__ __align__(16) float seam_sm[];   // [d] the row at hand, [d] the convolution's sums
+    __shared__ float red[33];
+    float* s_row = seam_sm;
+    float* s_acc = seam_sm + p.d;
+    const sllm_seq_batch& b = p.b;
+    const int t = blockIdx.x, d = p.d, slot = b.tok_slot[t], pos = b.tok_pos[t];
+    // the stash of the previous seam goes into that seam's ring before this launch overwrites the stash row
+    if (p.flush_ring && seam_is_last(b, t, slot, p.flush_taps - 1)) {
+        float* dst = p.flush_ring + ((size_t)slot * (p.flush_taps - 1) + pos % (p.flush_taps - 1)) * d;
+        for (int j = threadIdx.x; j < d; j += blockDim.x) dst[j] = p.stash[(size_t)t * d + j];
+    }
+    const int reach = (p.has_pre && p.conv_w) ? p.taps - 1 : 0;
+    bool started = false;                                // does s_acc hold a sum yet? (the same answer in every thread)
+    for (int back = reach; back >= 0; --back) {          // the current token last: its normed row stays in s_row
+        if (pos - back < 0) continue;                    // before the sequence's start: zeros
+        const bool here = back == 0 || (t - back >= 0 && b.tok_slot[t - back] == slot);
+        if (!here) {
+            const float* src = p.ring + ((size_t)slot * (p.taps - 1) + (pos - back) % (p.taps - 1)) * d;
+            for (int j = threadIdx.x; j < d; j += blockDim.x) {
+                s_acc[j] = fmaf(p.conv_w[(size_t)j * p.taps + p.taps - 1 - back], src[j], started ? s_acc[j] : 0.0f);
+            }
+            started = true;
+            continue;
+        }
+        const size_t r = (size_t)(t - back) * d;
+        float inv_y = 0.0f;
+        if (p.y) {
+            float ss = 0.0f;
+            for (int j = threadIdx.x; j < d; j += blockDim.x) ss = fmaf(p.y[r + j], p.y[r + j], ss);
+            inv_y = p.post_g / sqrtf(block_sum(ss, red) / (float)d + p.eps);
+        }
+        float ss = 0.0f;
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            float v = p.x_in[r + j];
+            if (p.y) {
+                v = fmaf(p.y[r + j], inv_y, v);
+                if (back == 0) p.x_out[r + j] = v;
+            }
+            s_row[j] = v;
+            ss = fmaf(v, v, ss);
+        }
+        if (!p.has_pre) return;
+        const float inv = p.pre_g / sqrtf(block_sum(ss, red) / (float)d + p.eps);
+        if (!p.conv_w) {
+            for (int j = threadIdx.x; j < d; j += blockDim.x) {
+                const float v = s_row[j] * inv;
+                p.h[r + j] = v;
+                if (p.h16) p.h16[r + j] = f32_to_bf16_bits(v);
+            }
+            return;
+        }
+        const bool keep = back == 0 && seam_is_last(b, t, slot, p.taps - 1);
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            const float n = s_row[j] * inv;
+            float acc = fmaf(p.conv_w[(size_t)j * p.taps + p.taps - 1 - back], n, started ? s_acc[j] : 0.0f);
+            if (back == 0) {
+                acc += n;
+                p.h[r + j] = acc;
+                if (p.h16) p.h16[r + j] = f32_to_bf16_bits(acc);
+                if (keep) p.stash[r + j] = n;
+            } else {
+                s_acc[j] = acc;
+            }
+        }
+        started = true;
+    }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+extern "C" int sllm_seq_seam(const sllm_seq_batch* b, const float* x_in, float* x_out, const float* y, float post_g, int32_t has_pre, float pre_g,
+                             float eps, const float* conv_w, int32_t taps, const float* ring, float* h, void* h16, float* stash, float* flush_ring,
+                             int32_t flush_taps, int32_t d, sllm_stream_t stream) {
+    SLLM_REQUIRE(b && b->T > 0 && b->tok_slot && b->tok_pos, SLLM_EINVAL, "seq_seam: incomplete batch description");
+    SLLM_REQUIRE(x_in && d > 0 && (!y || (x_out && x_out != x_in)), SLLM_EINVAL, "seq_seam: the residual sum needs a second buffer for x");
+    SLLM_REQUIRE(!has_pre || h, SLLM_EINVAL, "seq_seam: no output for the normed rows");
+    SLLM_REQUIRE(!conv_w || (taps >= 1 && taps <= 64 && (taps == 1 || (ring && stash))), SLLM_EINVAL, "seq_seam: a convolution needs its ring and a stash");
+    SLLM_REQUIRE(!flush_ring || (flush_taps >= 2 && stash), SLLM_EINVAL, "seq_seam: nothing to flush from");
+    if (conv_w && taps == 1) ring = nullptr;
+    const size_t smem = 2 * (size_t)d * sizeof(float);
+    SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes() - 1024, SLLM_ENOTSUP, "seq_seam: rows of %d floats do not fit shared memory", d);
+    if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_seam_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SeamArgs p{*b, x_in, x_out, y, post_g, has_pre, pre_g, eps, conv_w, taps, ring, h, (uint16_t*)h16, stash, flush_ring, flush_taps, d};
+    const int threads = b->T >= 64 ? (d >= 2048 ? 256 : 128) : std::min(1024, std::max(128, (d + 31) / 32 * 32));
+    seq_seam_kernel<<<b->T, threads, smem, as_stream(stream)>>>(p);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}

@@ -137,33 +137,61 @@ class LatentAttention:
     rot_dim outputs rotated by the position, a key part all heads share. Head h's key is (W_uk,h c, rotated part), its value W_uv,h c.
     Computed in the absorbed form, so that nothing but the cached row is read per key: the query of head h becomes (W_uk,h^T q_h, rotated
     q part) against the row itself (one key/value head of width kv_rank + rot_dim whose first kv_rank columns are also the value), and W_uv,h
-    is applied to the head's weighted sum of rows. The softmax's denominator holds exp(sink_h); head h's output is multiplied by
-    sigmoid(g_h); then the output projection."""
+    is applied to the head's weighted sum of rows. The softmax's denominator holds exp(sink_h) and head h's output is multiplied by
+    sigmoid(g_h) when the model has the tensors ``sink`` / ``g``; then the output projection.
+
+    Variants, chosen by the configuration and the tensors present: the queries may go through a latent of their own (``q_rank``:
+    q = W_uq RMSnorm(W_dq h), weight ``dq.norm``); the rotation's frequencies may be YaRN-scaled (``rot.scaling``; cos and sin then carry a
+    magnitude); with ``kv_from`` the layer has no down projection and attends over the rows another layer cached (its own W_uk / W_uv)."""
 
     def __init__(self, cfg, w, pre, ops, device, eps):
         self.cfg, self.ops, self.eps = cfg, ops, eps
         H, dn, dr, R = cfg.heads, cfg.dim, cfg.rot_dim, cfg.kv_rank
-        self.inputs = [(w[pre + "q"], w.get(pre + "q.b")), (w[pre + "dkv"], w.get(pre + "dkv.b")), (w[pre + "g"], w.get(pre + "g.b"))]
-        self.norm_w = w[pre + "dkv.norm"].float().contiguous()
+        self.q_latent = cfg.q_rank is not None
+        self.shared = cfg.kv_from is not None
+        self.gated = pre + "g" in w
+        self.inputs = [(w[pre + "dq"], w.get(pre + "dq.b"))] if self.q_latent else [(w[pre + "q"], w.get(pre + "q.b"))]
+        if not self.shared:
+            self.inputs.append((w[pre + "dkv"], w.get(pre + "dkv.b")))
+            self.norm_w = w[pre + "dkv.norm"].float().contiguous()
+        else:
+            self.norm_w = None
+        if self.gated:
+            self.inputs.append((w[pre + "g"], w.get(pre + "g.b")))
+        if self.q_latent:
+            self.q_norm_w = w[pre + "dq.norm"].float().contiguous()
+            self.uq = FusedLinear([(w[pre + "uq"], w.get(pre + "uq.b"))], ops, device)
         self.uk_t = w[pre + "uk"].view(H, dn, R).transpose(1, 2).contiguous()       # [H][R][dn]: rows of W_uk,h^T
         self.uv = w[pre + "uv"].contiguous()                                         # [H * vdim][R]
         self.sink = w[pre + "sink"].float().contiguous() if pre + "sink" in w else None
         self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
-        self.freq = torch.tensor([cfg.rot.base ** (-2.0 * i / cfg.rot.dims) for i in range(cfg.rot.dims // 2)], dtype=torch.float64, device=device)
+        f, self.magnitude = yarn_frequencies(cfg.rot.dims, cfg.rot.base, cfg.rot.scaling)
+        self.freq = torch.tensor(f, dtype=torch.float64, device=device)
         self.opts = ops.attention_options(cfg.mask.size, cfg.mask.keep_first, values_in_keys=True)
         self.width = H * cfg.vdim
 
     def state_spec(self):
+        if self.shared:       # no pool of its own: the state manager hands it the named layer's
+            return {"pages": [], "slots": [], "borrow": [("row", self.cfg.kv_from, "row")]}
         return {"pages": [("row", 1, self.cfg.kv_rank + self.cfg.rot_dim)], "slots": []}
 
     def forward(self, step, cols, ld, state, out):
         c, ops, T = self.cfg, self.ops, step.T
         H, dn, dr, R, dv = c.heads, c.dim, c.rot_dim, c.kv_rank, c.vdim
-        q, low, g = cols
+        cols = list(cols)
+        q, ldq = cols.pop(0), ld
+        low = None if self.shared else cols.pop(0)
+        g = cols.pop(0) if self.gated else None
+        if self.q_latent:                      # the query's own latent: norm in place, then the up projection of every head
+            ops.rmsnorm_rows(q, ld, self.q_norm_w, self.eps, q, ld, T, c.q_rank, step.st)
+            qfull = step.scratch("latent_qfull", T * self.uq.N)
+            self.uq(step, q, ld, qfull.data_ptr(), self.uq.N)
+            q, ldq = qfull.data_ptr(), self.uq.N
         wide = R + dr
         qa = step.scratch("latent_q", T * H * wide)
-        ops.latent_kv(step.b, q, ld, H, dn, dr, low, ld, R, self.norm_w, self.eps, self.freq, c.rot.dims // 2, qa, H * wide, state["row"], step.st)
-        ops.linear(q, ld, self.uk_t, dn, None, qa.data_ptr(), H * wide, T, R, dn, step.st, batch=H, a_bs=dn + dr, w_bs=R * dn, c_bs=wide)
+        ops.latent_kv(step.b, q, ldq, H, dn, dr, low, ld, R, self.norm_w, self.eps, self.freq, c.rot.dims // 2, qa, H * wide, state["row"], step.st,
+                      magnitude=self.magnitude)
+        ops.linear(q, ldq, self.uk_t, dn, None, qa.data_ptr(), H * wide, T, R, dn, step.st, batch=H, a_bs=dn + dr, w_bs=R * dn, c_bs=wide)
         ws = step.scratch("attn_ws", T * H * step.nsplit * (R + 2))
         ops.attention(step.b, qa.data_ptr(), H * wide, H, 1, wide, R, c.scale, state["row"], None, step.nsplit, ws, step.st, opts=self.opts)
         mixed = step.scratch("latent_o", T * H * R)
@@ -243,6 +271,76 @@ class GatedLinearAttention:
         ops.headnorm_gate(o.data_ptr(), self.width, g, ld, self.norm_w, c.heads, c.vdim, self.eps, out, self.width, T, step.st)
 
 
+class LogDistanceWindowAttention:
+    """Softmax attention without rotation over a paged cache: score = (q . k) * scale - r1_h * ln(1 + r2_h * distance) with two numbers
+    per head (tensors ``r1`` / ``r2``), a sliding window, grouped query heads, and a query temperature: the query at position p is
+    multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)."""
+
+    def __init__(self, cfg, w, pre, ops, device):
+        self.cfg, self.ops = cfg, ops
+        self.inputs = [(w[pre + "q"], w.get(pre + "q.b")), (w[pre + "k"], w.get(pre + "k.b")), (w[pre + "v"], w.get(pre + "v.b"))]
+        self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
+        self.logdist = torch.stack([w[pre + "r1"].float(), w[pre + "r2"].float()]).contiguous()      # [2][heads]
+        self.opts = ops.attention_options(cfg.mask.size, cfg.mask.keep_first, logdist=self.logdist)
+        self.width = cfg.heads * cfg.vdim
+
+    def state_spec(self):
+        return {"pages": [("k", self.cfg.kv_heads, self.cfg.dim), ("v", self.cfg.kv_heads, self.cfg.vdim)], "slots": []}
+
+    def forward(self, step, cols, ld, state, out):
+        c, ops = self.cfg, self.ops
+        q, k, v = cols
+        # the cache write of the mixers without rotation, with no head divided by anything; it also applies the query temperature
+        ops.unit_kv(step.b, q, ld, c.heads, c.dim, k, ld, c.kv_heads, v, ld, c.vdim, 0.0, 0, None, 0, 0.0, state["k"], state["v"], step.st,
+                    q_temp_coef=c.q_temp_coef, q_temp_every=c.q_temp_every)
+        ws = step.scratch("attn_ws", step.T * c.heads * step.nsplit * (c.vdim + 2))
+        ops.attention(step.b, q, ld, c.heads, c.kv_heads, c.dim, c.vdim, c.scale, state["k"], state["v"], step.nsplit, ws, step.st, opts=self.opts)
+        ops.attention_finish(step.b, ws, step.nsplit, c.heads, c.vdim, None, 0, None, 0, out, self.width, step.st)
+
+
+class GatedDeltaRule:
+    """Gated delta rule: q, k (``kv_heads`` heads of ``dim``) and v (``heads`` heads of ``vdim``) each pass a short causal convolution
+    (tensors ``<name>.conv``, no bias) and silu; q and k become unit vectors per head (q also times dim^-1/2); per head
+    S <- g S, u = beta (v - S^T k), S <- S + k u^T, o = S^T q with beta = sigmoid(W_b h) and g = exp(-exp(A_log) softplus(W_a h + dt_bias));
+    o is RMS-normed per head (weight ``norm`` shared by the heads), gated by silu(W_g h) and projected. State per sequence: S
+    [heads][dim][vdim] and the convolution's last taps-1 inputs (a ring indexed by position), fp32."""
+
+    unit_eps = 1e-6
+
+    def __init__(self, cfg, w, pre, ops, device, eps):
+        self.cfg, self.ops, self.eps = cfg, ops, eps
+        # q, k, v first and adjacent: one convolution runs over all their channels
+        self.inputs = [(w[pre + n], None) for n in ("q", "k", "v", "g", "b", "a")]
+        self.conv_w = torch.cat([w[pre + n + ".conv"].float() for n in ("q", "k", "v")], dim=0).contiguous()     # [channels][taps]
+        self.channels = int(self.conv_w.shape[0])
+        if int(self.conv_w.shape[1]) != cfg.conv:
+            raise ValueError(f"{pre}q.conv holds {int(self.conv_w.shape[1])} taps, the configuration says {cfg.conv}")
+        self.a_log = w[pre + "A_log"].float().contiguous()
+        self.dt_bias = w[pre + "dt_bias"].float().contiguous()
+        self.norm_w = w[pre + "norm"].float().contiguous()
+        self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
+        self.width = cfg.heads * cfg.vdim
+
+    def state_spec(self):
+        c = self.cfg
+        slots = [("S", (c.heads, c.dim, c.vdim))]
+        if c.conv > 1:
+            slots.append(("ring", (c.conv - 1, self.channels)))
+        return {"pages": [], "slots": slots}
+
+    def forward(self, step, cols, ld, state, out):
+        c, ops, T, C = self.cfg, self.ops, step.T, self.channels
+        q, k, v, g, bl, al = cols
+        u = step.scratch("delta_qkv", T * C)
+        ring = state.get("ring")
+        ops.conv_ring(step.b, q, ld, C, c.conv, self.conv_w, ring, 1, u, C, step.st)
+        nk = c.kv_heads * c.dim
+        o = step.scratch("delta_o", T * self.width)
+        ops.delta_rule(step.b, u.data_ptr(), C, u.data_ptr() + nk * F32B, C, u.data_ptr() + 2 * nk * F32B, C, bl, ld, al, ld, self.a_log, self.dt_bias,
+                       c.heads, c.kv_heads, c.dim, c.vdim, self.unit_eps, c.dim ** -0.5, state["S"], o, self.width, q, ld, C, c.conv, ring, step.st)
+        ops.headnorm_gate(o.data_ptr(), self.width, g, ld, self.norm_w, c.heads, c.vdim, self.eps, out, self.width, T, step.st)
+
+
 class MixerGroup:
     """One or more mechanisms reading the same input: their input projections run as one fused product, each mechanism's result goes
     through its own output projection, and the results are added with the given weights."""
@@ -258,11 +356,13 @@ class MixerGroup:
             i += len(m.inputs)
 
     def state_spec(self):
-        spec = {"pages": [], "slots": []}
+        spec = {"pages": [], "slots": [], "borrow": []}
         for name, m, _ in self.members:
             s = m.state_spec()
             spec["pages"] += [(f"{name}.{n}", g, wd) for n, g, wd in s["pages"]]
             spec["slots"] += [(f"{name}.{n}", shape) for n, shape in s["slots"]]
+            # (own name, layer run that owns the memory, its name there): the member of the same name in that layer's group
+            spec["borrow"] += [(f"{name}.{n}", run, f"{name}.{src}") for n, run, src in s.get("borrow", [])]
         return spec
 
     def forward(self, step, h, state, y, h16_ready=False):
@@ -320,3 +420,63 @@ class PolyNormFeedForward:
         self.up(step, h.data_ptr(), self.up.K, z.data_ptr(), n)
         self.ops.polynorm(z, n, self.coef, self.eps, z, n, T, n, step.st)
         self.down(step, z.data_ptr(), n, y.data_ptr(), self.down.N)
+
+
+class GatedFeedForward:
+    """W_down (silu(W_gate h) * (W_up h)): gate and up as one fused product, the activation leaves the down projection's bf16 operand rows
+    when that product runs on the tensor cores."""
+
+    def __init__(self, cfg, w, pre, ops, device):
+        self.ops = ops
+        self.up = FusedLinear([(w[pre + "gate"], w.get(pre + "gate.b")), (w[pre + "up"], w.get(pre + "up.b"))], ops, device)
+        self.down = FusedLinear([(w[pre + "down"], w.get(pre + "down.b"))], ops, device)
+        self.ff = cfg.ff
+
+    @property
+    def proj(self):
+        return self.up
+
+    def forward(self, step, h, y, h16_ready=False):
+        T, n = step.T, self.ff
+        z = step.scratch("ff_z", T * 2 * n)
+        self.up(step, h.data_ptr(), self.up.K, z.data_ptr(), 2 * n, a16_ready=h16_ready)
+        rows16 = self.down.operand_rows(step)
+        act = step.scratch("ff_act", T * n)        # fp32 rows; not written when the product reads the bf16 rows
+        self.ops.gated_act(z.data_ptr(), 2 * n, z.data_ptr() + n * F32B, 2 * n, None if rows16 is not None else act, n, T, n, step.st, out16=rows16)
+        self.down(step, act.data_ptr(), n, y.data_ptr(), self.down.N, a16_ready=rows16 is not None)
+
+
+class ExpertsFeedForward:
+    """Mixture of experts W_down,e act(W_up,e h) (tensors ``e<i>.up`` / ``e<i>.down``, no biases): router logits W_router h in fp32,
+    scores = softmax over ALL router outputs, the ``top`` largest (score + ``correction``) are chosen, the weights are the chosen scores
+    themselves; the last ``identity`` router outputs are experts whose output is h. Computed as two wide products: every expert's up
+    projection (and the router) side by side, the activation times the token's weight for that expert (zero if not chosen), and ONE down
+    product over the concatenated experts, added to (sum of the chosen identity scores) * h."""
+
+    activation = 0          # the exact (erf) gelu
+
+    def __init__(self, cfg, w, pre, ops, device):
+        self.cfg, self.ops = cfg, ops
+        E = cfg.experts
+        self.n_route = E + cfg.identity
+        if int(w[pre + "router"].shape[0]) != self.n_route:
+            raise ValueError(f"{pre}router has {int(w[pre + 'router'].shape[0])} outputs, the configuration names {self.n_route} experts")
+        self.correction = w[pre + "correction"].float().contiguous() if pre + "correction" in w else None
+        # experts first, router last: the experts' columns then start at a 16-byte boundary for every ff
+        self.up = FusedLinear([(w[f"{pre}e{e}.up"], None) for e in range(E)] + [(w[pre + "router"], None)], ops, device)
+        self.down = FusedLinear([(torch.cat([w[f"{pre}e{e}.down"] for e in range(E)], dim=1).contiguous(), None)], ops, device)
+        self.wide = E * cfg.ff
+
+    @property
+    def proj(self):
+        return self.up
+
+    def forward(self, step, h, y, h16_ready=False):
+        c, T, d, N = self.cfg, step.T, self.up.K, self.up.N
+        z = step.scratch("ff_z", T * N)
+        self.up(step, h.data_ptr(), d, z.data_ptr(), N, a16_ready=h16_ready)
+        rows16 = self.down.operand_rows(step)
+        act = step.scratch("ff_act", T * self.wide)   # fp32 rows; not written when the product reads the bf16 rows
+        self.ops.moe_act(z.data_ptr() + self.wide * F32B, N, self.n_route, c.experts, c.top, self.correction, z.data_ptr(), N, c.ff, self.activation,
+                         h, d, d, None if rows16 is not None else act, rows16, y, d, T, step.st)
+        self.down(step, act.data_ptr(), self.wide, y.data_ptr(), d, accumulate=True, a16_ready=rows16 is not None)

@@ -5,8 +5,9 @@ from __future__ import annotations
 from ..config import BF16, F32, read_model_config
 from .munazen import MunazenModel
 from .sopetar import SopetarModel
+from .vasosun import VasosunModel
 
-MODEL_CLASSES = {"Munazen": MunazenModel, "Sopetar": SopetarModel}
+MODEL_CLASSES = {"Munazen": MunazenModel, "Sopetar": SopetarModel, "Vasosun": VasosunModel}
 
 
 def build_model(model_dir: str, dtype: str = "bfloat16", device="cuda", build: bool = False):

@@ -37,6 +37,7 @@ class Step:
         self.b = _lib.SeqBatch()
         self.st = None
         self.nsplit = 1
+        self.prev_ids = None      # device array [T]: the token before each token in its sequence, -1 at a sequence's start
 
     def scratch(self, name: str, n_floats: int) -> torch.Tensor:
         return self.engine._scratch(name, n_floats)
@@ -69,9 +70,16 @@ class SequenceEngine:
             for name, shape in spec["slots"]:
                 st[name] = torch.zeros((max_seqs,) + tuple(shape), dtype=torch.float32, device=self.device)
             self.states.append(st)
+        # a layer may read state that another layer run owns (attention over an earlier layer's cache): one memory, two names
+        for st, spec in zip(self.states, model.state_specs()):
+            for name, run, src in spec.get("borrow", []):
+                if not 0 <= run < len(self.states) or src not in self.states[run]:
+                    raise ValueError(f"state {name!r} is borrowed from layer run {run}, which has no {src!r}")
+                st[name] = self.states[run][src]
         self._slot_tensors = [t for st, spec in zip(self.states, model.state_specs()) for name, _ in spec["slots"] for t in [st[name]]]
         self.free_slots = list(range(max_seqs - 1, -1, -1))
         self.pos = [0] * max_seqs
+        self.last_token = [-1] * max_seqs       # the token at position pos - 1 of each request (-1: none yet), part of its state
         self.live = set()
         self._bufs = {}
         self._meta_dev = None
@@ -95,6 +103,7 @@ class SequenceEngine:
         for t in self._slot_tensors:
             t[slot].zero_()
         self.pos[slot] = 0
+        self.last_token[slot] = -1
         self.live.add(slot)
         return slot
 
@@ -125,7 +134,7 @@ class SequenceEngine:
         total = sum(sizes)
         if self._meta_host is None or self._meta_host.numel() < total:
             # sized once for the largest step the pool can hold, so that the addresses captured in graphs stay valid
-            cap = max(total, 5 * self.max_len + 16 * self.max_seqs + self.max_seqs * self.max_pages + 64)
+            cap = max(total, 6 * self.max_len + 16 * self.max_seqs + self.max_seqs * self.max_pages + 64)
             self._graphs = {}
             self._meta_host = torch.empty(cap, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else torch.empty(cap, dtype=torch.int32)
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
@@ -164,6 +173,7 @@ class SequenceEngine:
         T = sum(t.size for _, t, _ in entries)
         nseg = len(entries)
         ids = np.concatenate([t for _, t, _ in entries])
+        prev_ids = np.concatenate([np.concatenate([[self.last_token[s]], t[:-1]]) for s, t, _ in entries]).astype(np.int32)
         tok_slot = np.concatenate([np.full(t.size, s, dtype=np.int32) for s, t, _ in entries])
         tok_pos = np.concatenate([np.arange(self.pos[s], self.pos[s] + t.size, dtype=np.int32) for s, t, _ in entries])
         seg_len = np.array([t.size for _, t, _ in entries], dtype=np.int32)
@@ -185,7 +195,7 @@ class SequenceEngine:
             if any(k < 0 or k >= t.size for k in w):
                 raise ValueError("a wanted index lies outside the entry's tokens")
         table = self.pages.table().astype(np.int32)
-        arrays = [ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, qt_seg, qt_off, rows if rows.size else np.zeros(1, np.int32), table, seg_tile0]
+        arrays = [ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, qt_seg, qt_off, rows if rows.size else np.zeros(1, np.int32), table, seg_tile0, prev_ids]
         p = self._upload(arrays)
         step = self.step_obj
         step.T, step.nseg = T, nseg
@@ -195,6 +205,7 @@ class SequenceEngine:
         b.qt_seg, b.qt_off, b.n_qtiles = p[7], p[8], int(qt_seg.size)
         b.block_table, b.max_pages, b.page_len = p[10], self.max_pages, self.page_len
         b.seg_tile0 = p[11]
+        step.prev_ids = _PtrView(p[12])
         ids_t = _PtrView(p[0])
         rows_t = _PtrView(p[9])
         n_rows = int(rows.size)
@@ -234,6 +245,7 @@ class SequenceEngine:
             logits = self.model.forward(step, ids_t, self.states, rows_t, n_rows, tap=tap)
         for slot, toks, _ in entries:
             self.pos[slot] += int(toks.size)
+            self.last_token[slot] = int(toks[-1])
         self.steps_run += 1
         return logits
 

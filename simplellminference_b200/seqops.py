@@ -88,19 +88,52 @@ class Ops:
         self._ck(self.lib.sllm_seq_attention_finish(C.byref(b), _p(ws), nsplit, heads, dv, _p(vfreq), layout, gate_ptr, ldg, _p(sink), _p(out), ldo, st))
 
     @staticmethod
-    def attention_options(window=0, keep_first=0, softcap=0.0, slopes=None, values_in_keys=False):
-        """The options structure of ``attention``; the caller keeps the ``slopes`` tensor alive."""
-        return _lib.SeqAttnOpts(int(window or 0), int(keep_first or 0), float(softcap or 0.0), _p(slopes), int(bool(values_in_keys)))
+    def attention_options(window=0, keep_first=0, softcap=0.0, slopes=None, values_in_keys=False, logdist=None):
+        """The options structure of ``attention``; the caller keeps the ``slopes`` and ``logdist`` tensors alive."""
+        return _lib.SeqAttnOpts(int(window or 0), int(keep_first or 0), float(softcap or 0.0), _p(slopes), int(bool(values_in_keys)), _p(logdist))
 
-    def unit_kv(self, b, q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, eps, unit, v_shared, share, lam, k_pool, v_pool, st):
+    def unit_kv(self, b, q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, eps, unit, v_shared, share, lam, k_pool, v_pool, st,
+                q_temp_coef=0.0, q_temp_every=0):
         self._ck(self.lib.sllm_seq_unit_kv(C.byref(b), q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, eps, unit, _p(v_shared), share, lam,
-                                           _p(k_pool), _p(v_pool), self.kv_dtype, st))
+                                           _p(k_pool), _p(v_pool), self.kv_dtype, q_temp_coef, q_temp_every, st))
 
-    def latent_kv(self, b, q_ptr, ldq, heads, dn, dr, low_ptr, ldlow, rank, norm_w, eps, freq, n_freq, q_out, ldqo, pool, st):
+    def latent_kv(self, b, q_ptr, ldq, heads, dn, dr, low_ptr, ldlow, rank, norm_w, eps, freq, n_freq, q_out, ldqo, pool, st, magnitude=1.0):
+        """``low_ptr`` None: nothing is cached (the pool belongs to another layer), only the queries' rotated parts are produced."""
         self._ck(self.lib.sllm_seq_latent_kv(C.byref(b), q_ptr, ldq, heads, dn, dr, low_ptr, ldlow, rank, _p(norm_w), eps, _p(freq), n_freq, _p(q_out),
-                                             ldqo, _p(pool), self.kv_dtype, st))
+                                             ldqo, _p(pool) if low_ptr else None, self.kv_dtype, magnitude, st))
+
+    # ---- scalar norms around sublayers that read through a short convolution ----
+    def embed_pair(self, ids, prev_ids, table, pairs, vocab, d, buckets, mul_prev, mul_cur, out, T, st):
+        self._ck(self.lib.sllm_seq_embed_pair(_p(ids), _p(prev_ids), _p(table), _p(pairs), self.w_dtype, vocab, d, buckets, mul_prev, mul_cur, _p(out), T, st))
+
+    def seam(self, b, x_in, d, st, x_out=None, y=None, post_g=1.0, pre_g=None, eps=0.0, conv_w=None, taps=1, ring=None, h=None, h16=None, stash=None,
+             flush_ring=None, flush_taps=0):
+        """x_out = x_in + post_g * y / rms(y) (if ``y``), then h = n + conv(n), n = pre_g * x / rms(x) (if ``pre_g`` is given)."""
+        self._ck(self.lib.sllm_seq_seam(C.byref(b), _p(x_in), _p(x_out), _p(y), post_g, int(pre_g is not None), pre_g or 0.0, eps, _p(conv_w), taps, _p(ring),
+                                        _p(h), _p(h16), _p(stash), _p(flush_ring), flush_taps, d, st))
+
+    def rmsnorm_rows(self, x_ptr, ldx, w, eps, y_ptr, ldy, T, n, st):
+        self._ck(self.lib.sllm_seq_rmsnorm_rows(x_ptr, ldx, _p(w), eps, y_ptr, ldy, T, n, st))
+
+    def gated_act(self, gate_ptr, ldg, up_ptr, ldu, out, ldo, T, n, st, out16=None, act=0):
+        self._ck(self.lib.sllm_seq_gated_act(gate_ptr, ldg, up_ptr, ldu, act, _p(out), ldo, _p(out16), T, n, st))
+
+    def softcap(self, x, n, cap, st):
+        self._ck(self.lib.sllm_seq_softcap(_p(x), n, cap, st))
+
+    def moe_act(self, logits_ptr, ldl, n_route, experts, top, correction, up_ptr, ldu, ff, act, h, ldh, d, out, out16, y, ldy, T, st, route_w=None):
+        self._ck(self.lib.sllm_seq_moe_act(logits_ptr, ldl, n_route, experts, top, _p(correction), up_ptr, ldu, ff, act, _p(h), ldh, d, _p(out), _p(out16),
+                                           _p(y), ldy, _p(route_w), T, st))
 
     # ---- recurrences ----
+    def conv_ring(self, b, x_ptr, ldx, channels, taps, w, ring, act, out, ldo, st):
+        self._ck(self.lib.sllm_seq_conv_ring(C.byref(b), x_ptr, ldx, channels, taps, _p(w), _p(ring), act, _p(out), ldo, st))
+
+    def delta_rule(self, b, q_ptr, ldq, k_ptr, ldk, v_ptr, ldv, beta_ptr, ldb, step_ptr, lda, a_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale,
+                   state, o, ldo, conv_x_ptr, ldx, channels, taps, ring, st):
+        self._ck(self.lib.sllm_seq_delta_rule(C.byref(b), q_ptr, ldq, k_ptr, ldk, v_ptr, ldv, beta_ptr, ldb, step_ptr, lda, _p(a_log), _p(dt_bias), heads,
+                                              kv_heads, dk, dv, unit_eps, qscale, _p(state), _p(o), ldo, conv_x_ptr, ldx, channels, taps, _p(ring), st))
+
     def conv(self, b, x_ptr, ldx, channels, taps, w, cb, tail, u, ldu, st):
         self._ck(self.lib.sllm_seq_conv(C.byref(b), x_ptr, ldx, channels, taps, _p(w), _p(cb), _p(tail), _p(u), ldu, st))
 
