@@ -69,6 +69,10 @@ def parse():
                     help="instead of the headline workload: prefill and decode throughput of the Sopetar design (windowed capped attention + latent attention, "
                          "parallel layers, depth-weighted average) beside the Llama engine at equal size; comma-separated sizes of "
                          "simplellminference_b200/bench_sopetar.py (w1024,w2048,w4096) or 'all'. One GPU; prints one JSON line {\"sopetar\": [...]}")
+    ap.add_argument("--vasosun", default=None, metavar="SIZES",
+                    help="instead of the headline workload: prefill and decode throughput of the Vasosun design (scalar-norm sublayers with an input convolution, "
+                         "window / latent attention, gated delta rule, mixture of experts) beside Sopetar and the Llama engine at equal size; comma-separated "
+                         "sizes of simplellminference_b200/bench_vasosun.py (w1024,w2048,w4096) or 'all'. One GPU; prints one JSON line {\"vasosun\": [...]}")
     ap.add_argument("--no-batch", action="store_true", help="(kept for old command lines: the secondary measurements are opt-in now, see --extras)")
     return ap.parse_args()
 
@@ -644,11 +648,14 @@ def main():
     real_stdout = os.dup(1)
     os.dup2(2, 1)
     sys.stdout = os.fdopen(real_stdout, "w", buffering=1)
-    if args.hybrid or args.sopetar:
+    if args.hybrid or args.sopetar or args.vasosun:
         import torch
         if args.hybrid:
             from simplellminference_b200 import bench_hybrid
             key, wanted = "hybrid", args.hybrid
+        elif args.vasosun:
+            from simplellminference_b200 import bench_vasosun as bench_hybrid
+            key, wanted = "vasosun", args.vasosun
         else:
             from simplellminference_b200 import bench_sopetar as bench_hybrid
             key, wanted = "sopetar", args.sopetar
