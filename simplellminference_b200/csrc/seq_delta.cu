@@ -2,8 +2,9 @@
 // of it. Per head the state S [dk][dv] (fp32, one per sequence slot) follows
 //     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 // with q and k made unit vectors per head (q also times dk^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) * softplus(a + dt_bias)).
-// Everything that enters the recurrence is fp32. The columns of S are independent recurrences that share k, q, beta and g: a thread
-// owns a piece (32 key channels) of one column in registers; the pieces of a column sit in adjacent lanes and meet by shuffles.
+// Everything that enters the recurrence is fp32. The columns of S are independent recurrences that share k, q, beta and g: a CTA takes
+// up to 32 columns of one head, a thread owns a piece (32 key channels) of one column in registers; the pieces of a column sit in
+// adjacent lanes and meet by shuffles. More CTAs per head means more of the machine per sequence: the token loop itself is serial.
 //
 // The convolution keeps its last taps-1 inputs per sequence in a ring (position p at row p % (taps-1)); the recurrence kernel, which
 // runs after the convolution has read the ring, stores the portion's last inputs there.
@@ -38,27 +39,29 @@ struct DeltaArgs {
     float* state;                                       // [slots][heads][dk][dv]
     float* o; int ldo;                                  // [T][heads * dv]
     const float* conv_x; int ldx, channels, taps; float* ring;   // inputs of the convolution, stored to the ring for the next step (NULL = not)
-    int chunk, PP;
+    int chunk, PP, CB;
 };
 
 constexpr int kDeltaKP = 32;      // key channels of a thread
-constexpr int kDeltaRS = kDeltaKP + 1;   // a piece's stride in shared memory (pieces of the same index then lie in different banks)
+constexpr int kDeltaRS = kDeltaKP + 4;   // a piece's stride in shared memory: 16-byte loads, pieces of the same index in different banks
+constexpr int kDeltaCB = 32;      // value columns of a CTA
 
-// CTA = (segment, head); thread = (value column j, piece `part` of the key channels), part = tid % PP
-__global__ void __launch_bounds__(1024) seq_delta_kernel(DeltaArgs p) {
-    extern __shared__ float dsm[];
+// CTA = (segment, head, block of CB value columns); thread = (value column j, piece `part` of the key channels), part = tid % PP
+template <int kMaxThreads>   // 256: the register budget holds the state piece, the keys and the sums; 1024 (very wide key heads): it spills
+__global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
+    extern __shared__ __align__(16) float dsm[];
     const sllm_seq_batch& b = p.b;
     const int seg = blockIdx.x, h = blockIdx.y, kvh = h / (p.heads / p.kv_heads);
     const int start = b.seg_start[seg], len = b.seg_len[seg], slot = b.seg_slot[seg], pos0 = b.seg_pos0[seg];
-    const int dk = p.dk, dv = p.dv, PP = p.PP, C = p.chunk, RS = PP * kDeltaRS;
-    const int part = threadIdx.x % PP, j = threadIdx.x / PP;
-    const bool live = j < dv;
+    const int dk = p.dk, dv = p.dv, PP = p.PP, C = p.chunk, RS = PP * kDeltaRS, CB = p.CB;
+    const int part = threadIdx.x % PP, jl = threadIdx.x / PP, j = blockIdx.z * CB + jl;   // jl: the column inside the CTA's block
+    const bool live = jl < CB && j < dv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     float* s_k = dsm;                 // [C][RS]
     float* s_q = s_k + C * RS;        // [C][RS]
-    float* s_v = s_q + C * RS;        // [C][dv]
-    float* s_o = s_v + C * dv;        // [C][dv]
-    float* s_beta = s_o + C * dv;     // [C]
+    float* s_v = s_q + C * RS;        // [C][CB]
+    float* s_o = s_v + C * CB;        // [C][CB]
+    float* s_beta = s_o + C * CB;     // [C]
     float* s_g = s_beta + C;          // [C]
     float* st = p.state + ((size_t)slot * p.heads + h) * dk * dv;
     float S[kDeltaKP];
@@ -77,7 +80,10 @@ __global__ void __launch_bounds__(1024) seq_delta_kernel(DeltaArgs p) {
             s_k[at] = kr < dk ? p.k[t * p.ldk + (size_t)kvh * dk + kr] : 0.0f;
             s_q[at] = kr < dk ? p.q[t * p.ldq + (size_t)kvh * dk + kr] : 0.0f;
         }
-        for (int i = threadIdx.x; i < n * dv; i += blockDim.x) s_v[i] = p.v[(size_t)(start + c0 + i / dv) * p.ldv + (size_t)h * dv + i % dv];
+        for (int i = threadIdx.x; i < n * CB; i += blockDim.x) {
+            const int col = blockIdx.z * CB + i % CB;
+            s_v[i] = col < dv ? p.v[(size_t)(start + c0 + i / CB) * p.ldv + (size_t)h * dv + col] : 0.0f;
+        }
         if (threadIdx.x < n) {
             const size_t t = (size_t)(start + c0 + threadIdx.x);
             s_beta[threadIdx.x] = seq_sigmoid(p.bl[t * p.ldb + h]);
@@ -101,27 +107,43 @@ __global__ void __launch_bounds__(1024) seq_delta_kernel(DeltaArgs p) {
         __syncthreads();
         for (int i = 0; i < n; ++i) {
             const float g = s_g[i], beta = s_beta[i];
-            const float* kk = s_k + i * RS + part * kDeltaRS;
-            const float* qq = s_q + i * RS + part * kDeltaRS;
-            float dot = 0.0f;
+            const float4* kk = reinterpret_cast<const float4*>(s_k + i * RS + part * kDeltaRS);
+            const float4* qq = reinterpret_cast<const float4*>(s_q + i * RS + part * kDeltaRS);
+            float kr[kDeltaKP];
+            float d4[4] = {0.0f, 0.0f, 0.0f, 0.0f};          // four running sums: no chain of 32 dependent multiply-adds
 #pragma unroll
-            for (int x = 0; x < kDeltaKP; ++x) {
-                S[x] *= g;
-                dot = fmaf(S[x], kk[x], dot);
+            for (int x = 0; x < kDeltaKP; x += 4) {
+                const float4 kv = kk[x >> 2];
+                kr[x] = kv.x; kr[x + 1] = kv.y; kr[x + 2] = kv.z; kr[x + 3] = kv.w;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    S[x + e] *= g;
+                    d4[e] = fmaf(S[x + e], kr[x + e], d4[e]);
+                }
             }
+            float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
             for (int o = PP >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const float u = beta * ((live ? s_v[i * dv + j] : 0.0f) - dot);
-            float out = 0.0f;
+            const float u = beta * ((live ? s_v[i * CB + jl] : 0.0f) - dot);
+            float o4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int x = 0; x < kDeltaKP; ++x) {
-                S[x] = fmaf(kk[x], u, S[x]);
-                out = fmaf(S[x], qq[x], out);
+            for (int x = 0; x < kDeltaKP; x += 4) {
+                const float4 qv = qq[x >> 2];
+                const float qr[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    S[x + e] = fmaf(kr[x + e], u, S[x + e]);
+                    o4[e] = fmaf(S[x + e], qr[e], o4[e]);
+                }
             }
+            float out = (o4[0] + o4[1]) + (o4[2] + o4[3]);
             for (int o = PP >> 1; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-            if (live && part == 0) s_o[i * dv + j] = out;
+            if (live && part == 0) s_o[i * CB + jl] = out;
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < n * dv; i += blockDim.x) p.o[(size_t)(start + c0 + i / dv) * p.ldo + (size_t)h * dv + i % dv] = s_o[i];
+        for (int i = threadIdx.x; i < n * CB; i += blockDim.x) {
+            const int col = blockIdx.z * CB + i % CB;
+            if (col < dv) p.o[(size_t)(start + c0 + i / CB) * p.ldo + (size_t)h * dv + col] = s_o[i];
+        }
         __syncthreads();
     }
     if (live) {
@@ -133,7 +155,7 @@ __global__ void __launch_bounds__(1024) seq_delta_kernel(DeltaArgs p) {
     }
     if (p.ring && p.taps > 1) {          // the heads of a segment share the job of storing its last inputs of the convolution
         const int keep = min(len, p.taps - 1);
-        for (int i = h * blockDim.x + threadIdx.x; i < keep * p.channels; i += p.heads * blockDim.x) {
+        for (int i = (h * gridDim.z + blockIdx.z) * blockDim.x + threadIdx.x; i < keep * p.channels; i += p.heads * gridDim.z * blockDim.x) {
             const int r = len - keep + i / p.channels, c = i % p.channels;
             p.ring[((size_t)slot * (p.taps - 1) + (pos0 + r) % (p.taps - 1)) * p.channels + c] = p.conv_x[(size_t)(start + r) * p.ldx + c];
         }
@@ -168,15 +190,17 @@ int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, co
     const int parts = (dk + kDeltaKP - 1) / kDeltaKP;
     int PP = 1;
     while (PP < parts) PP *= 2;
-    SLLM_REQUIRE(PP <= 32 && (long long)dv * PP <= 1024, SLLM_ENOTSUP, "seq_delta_rule: a %d x %d state does not fit one thread block (dk/32 * dv <= 1024)", dk, dv);
-    const int threads = (dv * PP + 31) / 32 * 32;
-    const int per_tok = 2 * PP * kDeltaRS + 2 * dv + 2;
+    SLLM_REQUIRE(PP <= 32, SLLM_ENOTSUP, "seq_delta_rule: key heads of %d channels beyond 1024", dk);
+    const int CB = std::min(dv, kDeltaCB), blocks = (dv + CB - 1) / CB;
+    const int threads = (CB * PP + 31) / 32 * 32;
+    const int per_tok = 2 * PP * kDeltaRS + 2 * CB + 2;
     const int chunk = std::max(1, std::min(16, 10240 / per_tok));
     const size_t smem = (size_t)chunk * per_tok * sizeof(float);
     SLLM_REQUIRE(smem <= 48 * 1024, SLLM_ENOTSUP, "seq_delta_rule: one token of a %d x %d head needs %zu bytes of shared memory", dk, dv, smem);
     DeltaArgs p{*b, q, k, v, ldq, ldk, ldv, beta_logit, step_logit, ldb, lda, A_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale, state, o, ldo,
-                conv_x, ldx, channels, taps, ring, chunk, PP};
-    seq_delta_kernel<<<dim3(b->nseg, heads), threads, smem, as_stream(stream)>>>(p);
+                conv_x, ldx, channels, taps, ring, chunk, PP, CB};
+    if (threads <= 256) seq_delta_kernel<256><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
+    else seq_delta_kernel<1024><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

@@ -40,13 +40,19 @@ def yarn_frequencies(dims: int, base: float, scaling: dict | None):
 
 class FusedLinear:
     """Several projections of the same input as ONE product: weight rows concatenated, one bias vector (zeros where a part has none).
-    ``offsets[i]`` is the first output column of part i."""
+    ``offsets[i]`` is the first output column of part i. ``pad_rows``: rows of zeros are appended until the row count is a multiple of it
+    (the tensor-core product takes output widths that are multiples of 4; the consumers of an input product address its columns
+    through pointers and the row stride ``N``, so the extra columns cost nothing but their zeros)."""
 
-    def __init__(self, parts, ops, device):
+    def __init__(self, parts, ops, device, pad_rows: int = 1):
         self.ops = ops
         self.K = int(parts[0][0].shape[1])
         self.sizes = [int(w.shape[0]) for w, _ in parts]
         self.offsets = [sum(self.sizes[:i]) for i in range(len(parts))]
+        pad = -sum(self.sizes) % max(1, pad_rows)
+        if pad:
+            parts = list(parts) + [(torch.zeros(pad, self.K, dtype=parts[0][0].dtype, device=parts[0][0].device), None)]
+            self.sizes = self.sizes + [pad]
         self.N = sum(self.sizes)
         self.w = torch.cat([w for w, _ in parts], dim=0).contiguous()
         if any(b is not None for _, b in parts):
@@ -349,7 +355,7 @@ class MixerGroup:
         self.members = members                       # [(name, mechanism, weight)]
         self.ops = ops
         parts = [p for _, m, _ in members for p in m.inputs]
-        self.proj = FusedLinear(parts, ops, device)
+        self.proj = FusedLinear(parts, ops, device, pad_rows=8)
         self.spans, i = [], 0
         for _, m, _ in members:
             self.spans.append(self.proj.offsets[i:i + len(m.inputs)])
@@ -428,7 +434,7 @@ class GatedFeedForward:
 
     def __init__(self, cfg, w, pre, ops, device):
         self.ops = ops
-        self.up = FusedLinear([(w[pre + "gate"], w.get(pre + "gate.b")), (w[pre + "up"], w.get(pre + "up.b"))], ops, device)
+        self.up = FusedLinear([(w[pre + "gate"], w.get(pre + "gate.b")), (w[pre + "up"], w.get(pre + "up.b"))], ops, device, pad_rows=8)
         self.down = FusedLinear([(w[pre + "down"], w.get(pre + "down.b"))], ops, device)
         self.ff = cfg.ff
 
@@ -438,11 +444,12 @@ class GatedFeedForward:
 
     def forward(self, step, h, y, h16_ready=False):
         T, n = step.T, self.ff
-        z = step.scratch("ff_z", T * 2 * n)
-        self.up(step, h.data_ptr(), self.up.K, z.data_ptr(), 2 * n, a16_ready=h16_ready)
+        N = self.up.N                              # 2 * ff, rounded up
+        z = step.scratch("ff_z", T * N)
+        self.up(step, h.data_ptr(), self.up.K, z.data_ptr(), N, a16_ready=h16_ready)
         rows16 = self.down.operand_rows(step)
         act = step.scratch("ff_act", T * n)        # fp32 rows; not written when the product reads the bf16 rows
-        self.ops.gated_act(z.data_ptr(), 2 * n, z.data_ptr() + n * F32B, 2 * n, None if rows16 is not None else act, n, T, n, step.st, out16=rows16)
+        self.ops.gated_act(z.data_ptr(), N, z.data_ptr() + n * F32B, N, None if rows16 is not None else act, n, T, n, step.st, out16=rows16)
         self.down(step, act.data_ptr(), n, y.data_ptr(), self.down.N, a16_ready=rows16 is not None)
 
 
@@ -463,7 +470,7 @@ class ExpertsFeedForward:
             raise ValueError(f"{pre}router has {int(w[pre + 'router'].shape[0])} outputs, the configuration names {self.n_route} experts")
         self.correction = w[pre + "correction"].float().contiguous() if pre + "correction" in w else None
         # experts first, router last: the experts' columns then start at a 16-byte boundary for every ff
-        self.up = FusedLinear([(w[f"{pre}e{e}.up"], None) for e in range(E)] + [(w[pre + "router"], None)], ops, device)
+        self.up = FusedLinear([(w[f"{pre}e{e}.up"], None) for e in range(E)] + [(w[pre + "router"], None)], ops, device, pad_rows=8)
         self.down = FusedLinear([(torch.cat([w[f"{pre}e{e}.down"] for e in range(E)], dim=1).contiguous(), None)], ops, device)
         self.wide = E * cfg.ff
 
