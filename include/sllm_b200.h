@@ -507,10 +507,11 @@ int sllm_seq_softcap(float* x, int64_t n, float cap, sllm_stream_t stream);
  * n = pre_g * x / rms(x), h = n + conv(n) with conv_w [d][taps] (last column = the current token; NULL = h = n) reaching back into
  * the step's rows and, before a portion, into ring [slots][taps-1][d] (position p at row p % (taps-1)); h16 (or NULL) = h as dense
  * bf16 rows; (3) the normed rows of every portion's last taps-1 tokens go to stash [T][d]; a later call with flush_ring (the ring this
- * call read) moves them there. rms(v) = sqrt(mean(v^2) + eps). */
+ * call read) moves them there. rms(v) = sqrt(mean(v^2) + eps). scales (or NULL): T floats of scratch; with it, steps of 64 tokens and
+ * more run as two launches (sum and per-row scale, then the convolution element-wise) so that no row is normed more than once. */
 int sllm_seq_seam(const sllm_seq_batch* b, const float* x_in, float* x_out, const float* y, float post_g, int32_t has_pre, float pre_g,
                   float eps, const float* conv_w, int32_t taps, const float* ring, float* h, void* h16, float* stash, float* flush_ring,
-                  int32_t flush_taps, int32_t d, sllm_stream_t stream);
+                  int32_t flush_taps, int32_t d, float* scales, sllm_stream_t stream);
 /* out[t][c] = act(sum_j w[c][j] * x[t - taps + 1 + j][c]) (act 0 = none, 1 = silu), zeros before a sequence's start; inputs before a
  * portion come from ring [slots][taps-1][channels] (position p at row p % (taps-1)), which is NOT updated here */
 int sllm_seq_conv_ring(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, const float* w, const float* ring,

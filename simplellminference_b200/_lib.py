@@ -148,7 +148,7 @@ SIGNATURES.update({
     "sllm_seq_rmsnorm_rows": (C.c_int, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
     "sllm_seq_gated_act": (C.c_int, [_P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _P]),
     "sllm_seq_softcap": (C.c_int, [_P, _L, _F, _P]),
-    "sllm_seq_seam": (C.c_int, [_B, _P, _P, _P, _F, _I, _F, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _P]),
+    "sllm_seq_seam": (C.c_int, [_B, _P, _P, _P, _F, _I, _F, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _P, _P]),
     "sllm_seq_conv_ring": (C.c_int, [_B, _P, _I, _I, _I, _P, _P, _I, _P, _I, _P]),
     "sllm_seq_delta_rule": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _F, _F, _P, _P, _I, _P, _I, _I, _I, _P, _P]),
     "sllm_seq_moe_act": (C.c_int, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P, _I, _P]),

@@ -39,16 +39,26 @@ struct DeltaArgs {
     float* state;                                       // [slots][heads][dk][dv]
     float* o; int ldo;                                  // [T][heads * dv]
     const float* conv_x; int ldx, channels, taps; float* ring;   // inputs of the convolution, stored to the ring for the next step (NULL = not)
-    int chunk, PP, CB;
+    int chunk, PP, CB, vec;
 };
 
-constexpr int kDeltaKP = 32;      // key channels of a thread
-constexpr int kDeltaRS = kDeltaKP + 4;   // a piece's stride in shared memory: 16-byte loads, pieces of the same index in different banks
-constexpr int kDeltaCB = 32;      // value columns of a CTA
+// key channels of a thread: 8 for key heads of up to 256 channels (a column's pieces fill up to a whole warp; the serial chain per token
+// is short), 32 for wider ones. A piece's stride in shared memory is 4 floats more: 16-byte loads, pieces of the same index in different banks.
+constexpr int kDeltaCB = 32;      // value columns of a CTA, at most
+
+__device__ __forceinline__ uint32_t delta_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// global -> shared without passing through registers; `take` false writes zeros and reads nothing
+__device__ __forceinline__ void delta_cp16(void* dst, const void* src, bool take) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(delta_smem(dst)), "l"(src), "r"(take ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void delta_cp4(void* dst, const void* src, bool take) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(delta_smem(dst)), "l"(src), "r"(take ? 4 : 0) : "memory");
+}
 
 // CTA = (segment, head, block of CB value columns); thread = (value column j, piece `part` of the key channels), part = tid % PP
-template <int kMaxThreads>   // 256: the register budget holds the state piece, the keys and the sums; 1024 (very wide key heads): it spills
+template <int kDeltaKP, int kMaxThreads>
 __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
+    constexpr int kDeltaRS = kDeltaKP + 4;
     extern __shared__ __align__(16) float dsm[];
     const sllm_seq_batch& b = p.b;
     const int seg = blockIdx.x, h = blockIdx.y, kvh = h / (p.heads / p.kv_heads);
@@ -57,12 +67,47 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
     const int part = threadIdx.x % PP, jl = threadIdx.x / PP, j = blockIdx.z * CB + jl;   // jl: the column inside the CTA's block
     const bool live = jl < CB && j < dv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    float* s_k = dsm;                 // [C][RS]
-    float* s_q = s_k + C * RS;        // [C][RS]
-    float* s_v = s_q + C * RS;        // [C][CB]
-    float* s_o = s_v + C * CB;        // [C][CB]
-    float* s_beta = s_o + C * CB;     // [C]
-    float* s_g = s_beta + C;          // [C]
+    // two stages of inputs (the next chunk of tokens travels while this one is walked), then what both share
+    const int CBp = (CB + 3) & ~3;                     // every array of a stage starts at a 16-byte boundary
+    const int stage_floats = C * (2 * RS + CBp + 4);   // per token: k and q [RS] each, v [CB], the two logits
+    float* s_o = dsm + 2 * stage_floats;               // [C][CB]
+    float* s_beta = s_o + C * CB;                      // [C]
+    float* s_g = s_beta + C;                           // [C]
+    const bool vec = p.vec;                            // 16-byte copies of q / k: dk a multiple of 4, rows 16-byte aligned
+    auto issue = [&](int c0, int stage) {
+        float* d_k = dsm + stage * stage_floats;
+        float* d_q = d_k + C * RS;
+        float* d_v = d_q + C * RS;
+        float* d_l = d_v + C * CBp;                    // [C][2] logits of beta and of the step
+        const int n = min(C, len - c0), groups = PP * kDeltaKP / 4;
+        for (int i = threadIdx.x; i < n * groups; i += blockDim.x) {               // channels beyond dk are zeros
+            const int tok = i / groups, kr = (i % groups) * 4;
+            const size_t t = (size_t)(start + c0 + tok);
+            const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + kr % kDeltaKP;
+            const float* ks = p.k + t * p.ldk + (size_t)kvh * dk;
+            const float* qs = p.q + t * p.ldq + (size_t)kvh * dk;
+            if (vec) {
+                delta_cp16(d_k + at, kr < dk ? ks + kr : ks, kr < dk);
+                delta_cp16(d_q + at, kr < dk ? qs + kr : qs, kr < dk);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    delta_cp4(d_k + at + e, kr + e < dk ? ks + kr + e : ks, kr + e < dk);
+                    delta_cp4(d_q + at + e, kr + e < dk ? qs + kr + e : qs, kr + e < dk);
+                }
+            }
+        }
+        for (int i = threadIdx.x; i < n * CB; i += blockDim.x) {
+            const int col = blockIdx.z * CB + i % CB;
+            const float* vs = p.v + (size_t)(start + c0 + i / CB) * p.ldv + (size_t)h * dv;
+            delta_cp4(d_v + i, col < dv ? vs + col : vs, col < dv);
+        }
+        if (threadIdx.x < 2 * n) {
+            const size_t t = (size_t)(start + c0 + (threadIdx.x >> 1));
+            delta_cp4(d_l + threadIdx.x, (threadIdx.x & 1) ? p.al + t * p.lda + h : p.bl + t * p.ldb + h, true);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
     float* st = p.state + ((size_t)slot * p.heads + h) * dk * dv;
     float S[kDeltaKP];
 #pragma unroll
@@ -71,35 +116,31 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
         S[x] = (live && kr < dk) ? st[(size_t)kr * dv + j] : 0.0f;
     }
     const float rate = expf(p.A_log[h]), bias = p.dt_bias[h];
-    for (int c0 = 0; c0 < len; c0 += C) {
+    issue(0, 0);
+    int stage = 0;
+    for (int c0 = 0; c0 < len; c0 += C, stage ^= 1) {
         const int n = min(C, len - c0);
-        for (int i = threadIdx.x; i < n * PP * kDeltaKP; i += blockDim.x) {        // channels beyond dk are zeros
-            const int tok = i / (PP * kDeltaKP), kr = i % (PP * kDeltaKP);
-            const size_t t = (size_t)(start + c0 + tok);
-            const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + kr % kDeltaKP;
-            s_k[at] = kr < dk ? p.k[t * p.ldk + (size_t)kvh * dk + kr] : 0.0f;
-            s_q[at] = kr < dk ? p.q[t * p.ldq + (size_t)kvh * dk + kr] : 0.0f;
-        }
-        for (int i = threadIdx.x; i < n * CB; i += blockDim.x) {
-            const int col = blockIdx.z * CB + i % CB;
-            s_v[i] = col < dv ? p.v[(size_t)(start + c0 + i / CB) * p.ldv + (size_t)h * dv + col] : 0.0f;
-        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                               // this chunk has landed for everyone, and everyone has left the chunk before
+        if (c0 + C < len) issue(c0 + C, stage ^ 1);
+        float* s_k = dsm + stage * stage_floats;       // [C][RS]
+        float* s_q = s_k + C * RS;                     // [C][RS]
+        const float* s_v = s_q + C * RS;               // [C][CB]
+        const float* s_l = s_v + C * CBp;              // [C][2]
         if (threadIdx.x < n) {
-            const size_t t = (size_t)(start + c0 + threadIdx.x);
-            s_beta[threadIdx.x] = seq_sigmoid(p.bl[t * p.ldb + h]);
-            s_g[threadIdx.x] = expf(-rate * seq_softplus(p.al[t * p.lda + h] + bias));
+            s_beta[threadIdx.x] = seq_sigmoid(s_l[2 * threadIdx.x]);
+            s_g[threadIdx.x] = expf(-rate * seq_softplus(s_l[2 * threadIdx.x + 1] + bias));
         }
-        __syncthreads();
         for (int tok = warp; tok < n; tok += nwarps) {                             // unit vectors: a warp per token
             float sk = 0.0f, sq = 0.0f;
-            for (int kr = lane; kr < PP * kDeltaKP; kr += 32) {                    // lane = offset in a piece, one piece per round
-                const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + lane;
+            for (int kr = lane; kr < PP * kDeltaKP; kr += 32) {
+                const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + kr % kDeltaKP;
                 sk = fmaf(s_k[at], s_k[at], sk);
                 sq = fmaf(s_q[at], s_q[at], sq);
             }
             const float ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps), iq = p.qscale / sqrtf(warp_sum(sq) + p.unit_eps);
             for (int kr = lane; kr < PP * kDeltaKP; kr += 32) {
-                const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + lane;
+                const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + kr % kDeltaKP;
                 s_k[at] *= ik;
                 s_q[at] *= iq;
             }
@@ -144,7 +185,6 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
             const int col = blockIdx.z * CB + i % CB;
             if (col < dv) p.o[(size_t)(start + c0 + i / CB) * p.ldo + (size_t)h * dv + col] = s_o[i];
         }
-        __syncthreads();
     }
     if (live) {
 #pragma unroll
@@ -187,20 +227,26 @@ int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, co
     SLLM_REQUIRE(q && k && v && beta_logit && step_logit && A_log && dt_bias && state && o, SLLM_EINVAL, "seq_delta_rule: bad argument");
     SLLM_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0, SLLM_EINVAL, "seq_delta_rule: %d heads over %d key heads", heads, kv_heads);
     SLLM_REQUIRE(!ring || (conv_x && channels > 0 && taps >= 1), SLLM_EINVAL, "seq_delta_rule: the ring needs the convolution's inputs");
-    const int parts = (dk + kDeltaKP - 1) / kDeltaKP;
+    const int KP = dk <= 256 ? 8 : 32, RSh = KP + 4;
+    const int parts = (dk + KP - 1) / KP;
     int PP = 1;
     while (PP < parts) PP *= 2;
     SLLM_REQUIRE(PP <= 32, SLLM_ENOTSUP, "seq_delta_rule: key heads of %d channels beyond 1024", dk);
-    const int CB = std::min(dv, kDeltaCB), blocks = (dv + CB - 1) / CB;
+    // value columns per CTA: as many as 32, fewer when the step would otherwise leave most of the machine idle (the token loop is serial)
+    int CB = std::min(dv, kDeltaCB);
+    while (CB > 8 && CB % 2 == 0 && (long long)b->nseg * heads * ((dv + CB - 1) / CB) < 2LL * sm_count()) CB /= 2;
+    const int blocks = (dv + CB - 1) / CB;
     const int threads = (CB * PP + 31) / 32 * 32;
-    const int per_tok = 2 * PP * kDeltaRS + 2 * CB + 2;
-    const int chunk = std::max(1, std::min(16, 10240 / per_tok));
+    const int per_tok = 2 * (2 * PP * RSh + ((CB + 3) & ~3) + 4) + CB + 2;      // two stages of inputs, one of outputs
+    const int chunk = std::max(1, std::min(16, 11264 / per_tok));
     const size_t smem = (size_t)chunk * per_tok * sizeof(float);
     SLLM_REQUIRE(smem <= 48 * 1024, SLLM_ENOTSUP, "seq_delta_rule: one token of a %d x %d head needs %zu bytes of shared memory", dk, dv, smem);
+    const int vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0;
     DeltaArgs p{*b, q, k, v, ldq, ldk, ldv, beta_logit, step_logit, ldb, lda, A_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale, state, o, ldo,
-                conv_x, ldx, channels, taps, ring, chunk, PP, CB};
-    if (threads <= 256) seq_delta_kernel<256><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
-    else seq_delta_kernel<1024><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
+                conv_x, ldx, channels, taps, ring, chunk, PP, CB, vec};
+    if (KP == 8) seq_delta_kernel<8, 1024><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
+    else if (threads <= 256) seq_delta_kernel<32, 256><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
+    else seq_delta_kernel<32, 1024><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

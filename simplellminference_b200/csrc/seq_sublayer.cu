@@ -99,13 +99,70 @@ __global__ void seq_seam_kernel(SeamArgs p) {
     }
 }
 
+// ---- the same seam as two launches, for steps of many tokens: no row is normed more than once ------------------------------------------
+// (1) one CTA per token: the residual sum and the scale of the next norm, scale[t] = g_pre / rms(x_new[t]);
+// (2) element-wise over (token, channel): h = n + conv(n) with n = scale * x_new read from the step's rows (complete after launch 1) or
+//     the ring, the stash and the flush as in the one-launch form.
+__global__ void seq_seam_sum_kernel(SeamArgs p, float* __restrict__ scale) {
+    extern __shared__ __align__(16) float seam_sm[];   // [d] the sublayer's output row
+    __shared__ float red[33];
+    const int t = blockIdx.x, d = p.d;
+    const size_t r = (size_t)t * d;
+    float ss = 0.0f;
+    if (p.y) {
+        float sy = 0.0f;
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            const float v = p.y[r + j];
+            seam_sm[j] = v;
+            sy = fmaf(v, v, sy);
+        }
+        const float inv_y = p.post_g / sqrtf(block_sum(sy, red) / (float)d + p.eps);
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            const float v = fmaf(seam_sm[j], inv_y, p.x_in[r + j]);
+            p.x_out[r + j] = v;
+            ss = fmaf(v, v, ss);
+        }
+    } else {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) ss = fmaf(p.x_in[r + j], p.x_in[r + j], ss);
+    }
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) scale[t] = p.pre_g / sqrtf(ss / (float)d + p.eps);
+}
+
+__global__ void seq_seam_conv_kernel(SeamArgs p, const float* __restrict__ scale) {
+    const sllm_seq_batch& b = p.b;
+    const int t = blockIdx.x, d = p.d, slot = b.tok_slot[t], pos = b.tok_pos[t], taps = p.taps;
+    const float* x = p.y ? p.x_out : p.x_in;             // the stream after the sum
+    const bool flush = p.flush_ring && seam_is_last(b, t, slot, p.flush_taps - 1);
+    const bool keep = seam_is_last(b, t, slot, taps - 1);
+    float* fdst = flush ? p.flush_ring + ((size_t)slot * (p.flush_taps - 1) + pos % (p.flush_taps - 1)) * d : nullptr;
+    const size_t r = (size_t)t * d;
+    const float own = scale[t];
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < d; j += gridDim.y * blockDim.x) {
+        if (flush) fdst[j] = p.stash[r + j];
+        float acc = 0.0f;
+        for (int back = taps - 1; back >= 1; --back) {
+            if (pos - back < 0) continue;
+            const bool here = t - back >= 0 && b.tok_slot[t - back] == slot;
+            const float n = here ? x[r - (size_t)back * d + j] * scale[t - back]
+                                 : p.ring[((size_t)slot * (taps - 1) + (pos - back) % (taps - 1)) * d + j];
+            acc = fmaf(p.conv_w[(size_t)j * taps + taps - 1 - back], n, acc);
+        }
+        const float n = x[r + j] * own;
+        acc = fmaf(p.conv_w[(size_t)j * taps + taps - 1], n, acc) + n;
+        p.h[r + j] = acc;
+        if (p.h16) p.h16[r + j] = f32_to_bf16_bits(acc);
+        if (keep) p.stash[r + j] = n;
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
 
 extern "C" int sllm_seq_seam(const sllm_seq_batch* b, const float* x_in, float* x_out, const float* y, float post_g, int32_t has_pre, float pre_g,
                              float eps, const float* conv_w, int32_t taps, const float* ring, float* h, void* h16, float* stash, float* flush_ring,
-                             int32_t flush_taps, int32_t d, sllm_stream_t stream) {
+                             int32_t flush_taps, int32_t d, float* scales, sllm_stream_t stream) {
     SLLM_REQUIRE(b && b->T > 0 && b->tok_slot && b->tok_pos, SLLM_EINVAL, "seq_seam: incomplete batch description");
     SLLM_REQUIRE(x_in && d > 0 && (!y || (x_out && x_out != x_in)), SLLM_EINVAL, "seq_seam: the residual sum needs a second buffer for x");
     SLLM_REQUIRE(!has_pre || h, SLLM_EINVAL, "seq_seam: no output for the normed rows");
@@ -117,6 +174,13 @@ extern "C" int sllm_seq_seam(const sllm_seq_batch* b, const float* x_in, float* 
     if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_seam_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     SeamArgs p{*b, x_in, x_out, y, post_g, has_pre, pre_g, eps, conv_w, taps, ring, h, (uint16_t*)h16, stash, flush_ring, flush_taps, d};
     const int threads = b->T >= 64 ? (d >= 2048 ? 256 : 128) : std::min(1024, std::max(128, (d + 31) / 32 * 32));
+    if (scales && has_pre && conv_w && b->T >= 64 && b->T <= 65535) {       // many tokens: two launches, every row normed once
+        seq_seam_sum_kernel<<<b->T, threads, smem / 2, as_stream(stream)>>>(p, scales);
+        seq_seam_conv_kernel<<<dim3(b->T, std::max(1, std::min(8, d / 1024))), 256, 0, as_stream(stream)>>>(p, scales);
+        g_launches += 2;
+        SLLM_LAUNCH_CHECK();
+        return SLLM_OK;
+    }
     seq_seam_kernel<<<b->T, threads, smem, as_stream(stream)>>>(p);
     ++g_launches;
     SLLM_LAUNCH_CHECK();

@@ -69,6 +69,7 @@ class VasosunModel:
         h = step.scratch("normed", T * d)
         y = step.scratch("sub_out", T * d)
         stash = step.scratch("conv_stash", T * d) if self.taps > 1 else None
+        scales = step.scratch("seam_scales", T)
         if self.pairs is not None:
             ops.embed_pair(ids, step.prev_ids, self.embed, self.pairs, self.vocab, d, c.pair_buckets, c.pair_mul_prev, c.pair_mul_cur, xa, T, step.st)
         else:
@@ -87,7 +88,7 @@ class VasosunModel:
                 prev = None
             ops.seam(step.b, xa, d, step.st, x_out=xb if prev is not None else None, y=y if prev is not None else None,
                      post_g=prev.post_g if prev is not None else 1.0, pre_g=sub.pre_g, eps=c.norm_eps, conv_w=sub.conv_w, taps=self.taps, ring=ring, h=h,
-                     h16=h16, stash=stash, flush_ring=prev_ring, flush_taps=self.taps if prev_ring is not None else 0)
+                     h16=h16, stash=stash, flush_ring=prev_ring, flush_taps=self.taps if prev_ring is not None else 0, scales=scales)
             if prev is not None:
                 xa, xb = xb, xa
             if sub.name == "mix":

@@ -107,10 +107,10 @@ class Ops:
         self._ck(self.lib.sllm_seq_embed_pair(_p(ids), _p(prev_ids), _p(table), _p(pairs), self.w_dtype, vocab, d, buckets, mul_prev, mul_cur, _p(out), T, st))
 
     def seam(self, b, x_in, d, st, x_out=None, y=None, post_g=1.0, pre_g=None, eps=0.0, conv_w=None, taps=1, ring=None, h=None, h16=None, stash=None,
-             flush_ring=None, flush_taps=0):
+             flush_ring=None, flush_taps=0, scales=None):
         """x_out = x_in + post_g * y / rms(y) (if ``y``), then h = n + conv(n), n = pre_g * x / rms(x) (if ``pre_g`` is given)."""
         self._ck(self.lib.sllm_seq_seam(C.byref(b), _p(x_in), _p(x_out), _p(y), post_g, int(pre_g is not None), pre_g or 0.0, eps, _p(conv_w), taps, _p(ring),
-                                        _p(h), _p(h16), _p(stash), _p(flush_ring), flush_taps, d, st))
+                                        _p(h), _p(h16), _p(stash), _p(flush_ring), flush_taps, d, _p(scales), st))
 
     def rmsnorm_rows(self, x_ptr, ldx, w, eps, y_ptr, ldy, T, n, st):
         self._ck(self.lib.sllm_seq_rmsnorm_rows(x_ptr, ldx, _p(w), eps, y_ptr, ldy, T, n, st))

@@ -136,7 +136,7 @@ def _mixer_stub(layer_cfgs, w, width, dtype="float32", eps=1e-5):
 ALONE = [L.attention_layer(), L.attention_layer(heads=3, kv_heads=3, dim=20, vdim=36, size=9, every=0), L.attention_layer(heads=8, kv_heads=1, dim=8, vdim=8, size=64, scale=1.0, every=2),
          L.attention_layer(size=None), L.latent_layer(), L.latent_layer(heads=1, dim=24, rot_dim=4, vdim=70, kv_rank=72, q_rank=5),
          L.latent_layer(heads=5, dim=4, rot_dim=16, rot_dims=6, vdim=12, kv_rank=20, scaling=None), L.delta_layer(), L.delta_layer(heads=1, kv_heads=1, dim=100, vdim=5, conv=1),
-         L.delta_layer(heads=6, kv_heads=2, dim=8, vdim=33, conv=6)]
+         L.delta_layer(heads=6, kv_heads=2, dim=8, vdim=33, conv=6), L.delta_layer(heads=2, kv_heads=1, dim=300, vdim=5, conv=2)]
 
 
 def _oracle_mixer(layer_cfg, w, h, pre="l0.mix.", kv=None):
@@ -277,7 +277,7 @@ def test_seam_kernel_alone():
     from simplellminference_b200.config import F32
     from simplellminference_b200.seqops import Ops
     rng, dev, ops = np.random.default_rng(2), torch.device("cuda"), Ops(F32)
-    for d, taps, T in ((48, 3, 40), (1000, 4, 19), (50, 1, 9), (36, 7, 30)):
+    for d, taps, T in ((48, 3, 40), (1000, 4, 19), (50, 1, 9), (36, 7, 30), (52, 3, 150)):
         x, y = (3 * rng.standard_normal((T, d))).astype(np.float32), rng.standard_normal((T, d)).astype(np.float32)
         cw = (0.5 * rng.standard_normal((d, taps))).astype(np.float32)
         g_post, g_pre, eps = 0.8, 1.3, 1e-5
@@ -295,13 +295,15 @@ def test_seam_kernel_alone():
                     ops.seam(step.b, xi, d, step.st, x_out=xo, y=yi, post_g=g_post, eps=eps)
                     ops.seam(step.b, xo, d, step.st, pre_g=g_pre, eps=eps, conv_w=cwt, taps=taps, ring=ring, h=ho, stash=stash)
                 else:
-                    ops.seam(step.b, xi, d, step.st, x_out=xo, y=yi, post_g=g_post, pre_g=g_pre, eps=eps, conv_w=cwt, taps=taps, ring=ring, h=ho, stash=stash)
+                    # with scratch for the per-row scales, steps of 64 tokens and more take the two-launch form
+                    ops.seam(step.b, xi, d, step.st, x_out=xo, y=yi, post_g=g_post, pre_g=g_pre, eps=eps, conv_w=cwt, taps=taps, ring=ring, h=ho, stash=stash,
+                             scales=step.scratch("scales", n))
                 tail = torch.empty_like(xi)
                 ops.seam(step.b, xo, d, step.st, pre_g=1.0, eps=eps, h=tail, stash=stash, flush_ring=ring, flush_taps=taps if ring is not None else 0)
                 return [xo, ho]
             spec = {"pages": [], "slots": [("ring", (taps - 1, d))] if taps > 1 else []}
             stub = _Stub([spec], fn, ops, dev)
-            for portions in ([T], [1] * T, [2, 1, 3, T - 6]):
+            for portions in ([T], [1] * T, [2, 1, 3, T - 6], [T - 3, 3]):
                 got = _feed(stub, np.concatenate([x, y], axis=1), portions)
                 assert _rel(got[0], x_new) < 1e-6 and _rel(got[1], want) < 2e-6, (d, taps, split, portions[:3], _rel(got[1], want))
 
