@@ -432,10 +432,12 @@ int sllm_seq_hyper_write_read(float* x, int32_t streams, int32_t T, int32_t d, c
  * (block-diagonal matrices). Any T, N, K. With a16 (scratch of T*K bf16 values) given, bf16 weights and a shape its tiles take, the
  * product runs on the tensor cores (tcgen05); otherwise on fp32 FMAs. a16_ready != 0: the kernel that produced A has already left
  * its rows in a16 as dense bf16 [T][K] (sllm_seq_depth_average, sllm_seq_layernorm and sllm_seq_clamped_glu can), so that the copy is
- * skipped; only meaningful when sllm_seq_linear_on_tensor_cores says the product goes there. */
+ * skipped; only meaningful when sllm_seq_linear_on_tensor_cores says the product goes there. rows_dev (device memory or NULL): a row
+ * count an earlier kernel left; rows from *rows_dev on (of the T the call names) are not computed and their outputs stay as they are
+ * (steps of more than 8 tokens; smaller steps compute all T rows). */
 int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32_t w_dtype, int32_t ldw, const float* bias, float* C, int32_t ldc,
                     int32_t T, int32_t N, int32_t K, float alpha, int32_t accumulate, int32_t round_a, int32_t batch, int64_t a_bs,
-                    int64_t w_bs, int64_t bias_bs, int64_t c_bs, void* a16, int32_t a16_ready, sllm_stream_t stream);
+                    int64_t w_bs, int64_t bias_bs, int64_t c_bs, void* a16, int32_t a16_ready, const int32_t* rows_dev, sllm_stream_t stream);
 /* 1 when sllm_seq_linear with a bf16 scratch sends this shape to the tensor cores (the weights must also be 16-byte aligned) */
 int sllm_seq_linear_on_tensor_cores(int32_t T, int32_t N, int32_t K, int32_t w_dtype, int32_t ldw, int32_t batch, int32_t round_a);
 /* PolyNorm: out = c0*N(z) + c1*N(z^2) + c2*N(z^3) + c3, powers element-wise, N(v) = v / sqrt(mean(v^2) + eps) over a row; coef: 4 floats */
@@ -532,6 +534,21 @@ int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, co
 int sllm_seq_moe_act(const float* logits, int32_t ldl, int32_t n_route, int32_t experts, int32_t top, const float* correction, const float* up,
                      int32_t ldu, int32_t ff, int32_t act, const float* h, int32_t ldh, int32_t d, float* out, void* out16, float* y,
                      int32_t ldy, float* route_w, int32_t T, sllm_stream_t stream);
+/* The same layer with the tokens gathered per expert, for steps of many tokens. sllm_seq_moe_route: routing as above; every (token,
+ * chosen expert with weights) pair takes the next free row of that expert's buffer (counts [experts] int32, zeroed before the call;
+ * buffers of cap >= T rows) and the token's input row h is copied there as bf16 (rows16 [experts][cap][d]) and / or fp32 (rows32);
+ * sel_e / sel_pos / sel_w [T][top] = expert (-1: none), row and score of each choice, ident [T] = the sum of the chosen identity scores.
+ * Which row a pair gets depends on timing; the numbers in it do not. sllm_seq_moe_expert_act: act over the rows in use of
+ * up [experts][cap][ff]. sllm_seq_moe_combine: y[t] = ident[t] * h[t] + sum_k sel_w * down[sel_e][sel_pos] (down [experts][cap][d]). */
+int sllm_seq_moe_route(const float* logits, int32_t ldl, int32_t n_route, int32_t experts, int32_t top, const float* correction, const float* h,
+                       int32_t ldh, int32_t d, int32_t* counts, int32_t cap, int32_t* sel_e, int32_t* sel_pos, float* sel_w, float* ident,
+                       void* rows16, float* rows32, int32_t T, sllm_stream_t stream);
+int sllm_seq_moe_expert_act(const float* up, const int32_t* counts, int32_t experts, int32_t cap, int32_t ff, int32_t act, void* out16,
+                            float* out32, sllm_stream_t stream);
+int sllm_seq_moe_combine(const float* down, const int32_t* sel_e, const int32_t* sel_pos, const float* sel_w, int32_t top, const float* ident,
+                         const float* h, int32_t ldh, int32_t cap, int32_t d, float* y, int32_t ldy, int32_t T, sllm_stream_t stream);
+/* n_bytes of zeros at p, in stream order */
+int sllm_seq_zero(void* p, int64_t n_bytes, sllm_stream_t stream);
 /* y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + bias per row (bias NULL = none); y16 (or NULL): the same rows once more, rounded
  * to bf16, dense [T][d] — the operand copy of a tensor-core product that follows */
 int sllm_seq_layernorm(const float* x, int32_t ldx, const float* w, const float* bias, float eps, float* y, int32_t ldy, void* y16,

@@ -37,6 +37,7 @@ struct PfGemmArgs {
     int32_t I_loc;
     int32_t bn;           // 0 = choose; 128 / 256 = force the N tile
     const float* bias;    // STORE / RESID / ACCUM: fp32 [N] added to every row of C (once, whatever the split of K), or NULL
+    const int32_t* rows_dev;   // device memory or NULL: only the first *rows_dev rows of A (at most T) are multiplied — a count an earlier kernel left
 };
 
 struct PfCache;   // tensor-map cache (one CUtensorMap per weight matrix and tile shape), owned by the engine

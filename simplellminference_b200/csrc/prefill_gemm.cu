@@ -56,6 +56,7 @@ struct PfDev {           // kernel-side view of PfGemmArgs
     const float *sin_t, *cos_t;
     uint16_t* s_out; int32_t I_loc;
     const float* bias;
+    const int32_t* rows_dev;   // the row tiles beyond ceil(*rows_dev / tile rows) are skipped by every role alike
 };
 
 // ------------------------------------------------------------------------------------------ PTX -------
@@ -342,11 +343,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
     if (PAIR) cluster_sync_all(); else __syncthreads();   // pair: the peer's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int nunits = p.m_tiles * p.n_tiles * p.ksplit;
     // programmatic dependent launch: everything above overlapped the previous kernel's tail; its results (A, the residual
     // stream) are visible after the wait. The next kernel may start ITS set-up as soon as every CTA here is past this point.
     pdl_wait();
     pdl_launch_dependents();
+    // a row count left by an earlier kernel (tokens routed to one expert): every thread reads the same number, so the three roles walk the
+    // same work units; with no rows at all the kernel only tears down
+    int m_tiles = p.m_tiles;
+    if (p.rows_dev) m_tiles = min(m_tiles, (*p.rows_dev + BM - 1) / BM);
+    const int nunits = m_tiles * p.n_tiles * p.ksplit;
 
     if (warp == 0) {
         if (lane == 0) {   // ===== TMA producer =====
@@ -355,7 +360,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
             for (int unit = worker; unit < nunits; unit += nworkers) {
                 const int tile = unit / p.ksplit, part = unit - tile * p.ksplit;
                 const int kb0 = (p.nkb * part) / p.ksplit, kb1 = (p.nkb * (part + 1)) / p.ksplit;
-                const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;   // consecutive workers share the weight tile (L2)
+                const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;   // consecutive workers share the weight tile (L2)
                 const int row0 = m_tile * BM + (int)rank * kPfBM;                  // this CTA's 128 rows of A
                 const int n0 = n_tile * BN + (int)rank * b_rows;                   // this CTA's rows of W
                 for (int kb = kb0; kb < kb1; ++kb) {
@@ -416,7 +421,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pf_gemm_kernel(const __grid_con
         const uint32_t tempty_leader[2] = {PAIR ? mapa_u32(tempty, 0) : 0u, PAIR ? mapa_u32(tempty + 1, 0) : 0u};
         for (int unit = worker; unit < nunits; unit += nworkers) {
             const int tile = unit / p.ksplit;
-            const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+            const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
             const int t = m_tile * BM + (int)rank * kPfBM + row;
             mb_wait(tfull + acc, acc_phase);
             tc_fence_after();
@@ -581,6 +586,7 @@ int pf_gemm(PfCache* cache, const PfGemmArgs& a, cudaStream_t st) {
     p.q_out = a.q_out; p.kc = a.k_cache; p.vc = a.v_cache; p.kv_dtype = a.kv_dtype; p.q_loc = a.q_loc; p.kv_loc = a.kv_loc; p.hd = a.hd; p.S = a.S;
     p.pos0 = a.pos0; p.sin_t = a.sin_t; p.cos_t = a.cos_t; p.s_out = a.s_out; p.I_loc = a.I_loc;
     p.bias = (a.epilogue == PF_EPI_STORE || a.epilogue == PF_EPI_RESID || a.epilogue == PF_EPI_ACCUM) ? a.bias : nullptr;
+    p.rows_dev = a.rows_dev;
 
     CUtensorMap tmA;
     {

@@ -8,6 +8,8 @@
 //
 // The convolution keeps its last taps-1 inputs per sequence in a ring (position p at row p % (taps-1)); the recurrence kernel, which
 // runs after the convolution has read the ring, stores the portion's last inputs there.
+#include <cstdlib>
+
 #include "seq_common.cuh"
 
 namespace sllm {
@@ -42,8 +44,8 @@ struct DeltaArgs {
     int chunk, PP, CB, vec;
 };
 
-// key channels of a thread: 8 for key heads of up to 256 channels (a column's pieces fill up to a whole warp; the serial chain per token
-// is short), 32 for wider ones. A piece's stride in shared memory is 4 floats more: 16-byte loads, pieces of the same index in different banks.
+// key channels of a thread: 16 for key heads of up to 512 channels (measured best of 8 / 16 / 32 at 128-wide heads), 32 for wider ones.
+// A piece's stride in shared memory is 4 floats more: 16-byte loads, pieces of the same index in different banks.
 constexpr int kDeltaCB = 32;      // value columns of a CTA, at most
 
 __device__ __forceinline__ uint32_t delta_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -227,14 +229,19 @@ int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, co
     SLLM_REQUIRE(q && k && v && beta_logit && step_logit && A_log && dt_bias && state && o, SLLM_EINVAL, "seq_delta_rule: bad argument");
     SLLM_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0, SLLM_EINVAL, "seq_delta_rule: %d heads over %d key heads", heads, kv_heads);
     SLLM_REQUIRE(!ring || (conv_x && channels > 0 && taps >= 1), SLLM_EINVAL, "seq_delta_rule: the ring needs the convolution's inputs");
-    const int KP = dk <= 256 ? 8 : 32, RSh = KP + 4;
+    static const int tune_kp = getenv("SLLM_DELTA_KP") ? atoi(getenv("SLLM_DELTA_KP")) : 0;      // measurement aids: 8 / 16 / 32 channels per thread,
+    static const int tune_cb = getenv("SLLM_DELTA_CB") ? atoi(getenv("SLLM_DELTA_CB")) : 0;      // columns per CTA
+    int KP = dk <= 512 ? 16 : 32;
+    if ((tune_kp == 8 || tune_kp == 16 || tune_kp == 32) && (dk + tune_kp - 1) / tune_kp <= 32) KP = tune_kp;
+    const int RSh = KP + 4;
     const int parts = (dk + KP - 1) / KP;
     int PP = 1;
     while (PP < parts) PP *= 2;
     SLLM_REQUIRE(PP <= 32, SLLM_ENOTSUP, "seq_delta_rule: key heads of %d channels beyond 1024", dk);
-    // value columns per CTA: as many as 32, fewer when the step would otherwise leave most of the machine idle (the token loop is serial)
+    // value columns per CTA: 32 measured best whatever the number of heads (the token loop is serial and bound by its own latency:
+    // narrower CTAs only add warps that wait)
     int CB = std::min(dv, kDeltaCB);
-    while (CB > 8 && CB % 2 == 0 && (long long)b->nseg * heads * ((dv + CB - 1) / CB) < 2LL * sm_count()) CB /= 2;
+    if (tune_cb > 0) CB = std::min(dv, tune_cb);
     const int blocks = (dv + CB - 1) / CB;
     const int threads = (CB * PP + 31) / 32 * 32;
     const int per_tok = 2 * (2 * PP * RSh + ((CB + 3) & ~3) + 4) + CB + 2;      // two stages of inputs, one of outputs
@@ -245,6 +252,7 @@ int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, co
     DeltaArgs p{*b, q, k, v, ldq, ldk, ldv, beta_logit, step_logit, ldb, lda, A_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale, state, o, ldo,
                 conv_x, ldx, channels, taps, ring, chunk, PP, CB, vec};
     if (KP == 8) seq_delta_kernel<8, 1024><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
+    else if (KP == 16) seq_delta_kernel<16, 512><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
     else if (threads <= 256) seq_delta_kernel<32, 256><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
     else seq_delta_kernel<32, 1024><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
     ++g_launches;

@@ -19,6 +19,7 @@ struct LinArgs {
     int lda, ldw, ldc, T, N, K, w_dtype, accumulate, round_a;
     float alpha;
     long long a_bs, w_bs, bias_bs, c_bs;
+    const int32_t* rows_dev;   // device memory or NULL: rows from *rows_dev on are not computed (tile body and tensor cores)
 };
 
 constexpr int kRowsMax = 8;
@@ -136,6 +137,7 @@ __global__ void __launch_bounds__(256) seq_linear_tile_kernel(LinArgs p) {
     const float* bias = p.bias ? p.bias + (size_t)b * p.bias_bs : nullptr;
     float* C = p.C + (size_t)b * p.c_bs;
     const int m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
+    if (p.rows_dev && m0 >= *p.rows_dev) return;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 4;   // loader: row lr of the tile, k columns lk .. lk+3
     float acc[4][4];
@@ -221,12 +223,12 @@ extern "C" int sllm_seq_linear_on_tensor_cores(int32_t T, int32_t N, int32_t K, 
 
 extern "C" int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32_t w_dtype, int32_t ldw, const float* bias, float* C, int32_t ldc, int32_t T,
                                int32_t N, int32_t K, float alpha, int32_t accumulate, int32_t round_a, int32_t batch, int64_t a_bs, int64_t w_bs,
-                               int64_t bias_bs, int64_t c_bs, void* a16, int32_t a16_ready, sllm_stream_t stream) {
+                               int64_t bias_bs, int64_t c_bs, void* a16, int32_t a16_ready, const int32_t* rows_dev, sllm_stream_t stream) {
     SLLM_REQUIRE(A && W && C && T > 0 && N > 0 && K > 0 && batch >= 1, SLLM_EINVAL, "seq_linear: bad argument");
     SLLM_REQUIRE(lda >= K && ldw >= K && ldc >= N, SLLM_EINVAL, "seq_linear: row strides shorter than the rows");
     SLLM_REQUIRE(w_dtype == SLLM_F32 || w_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_linear: fp32 or bf16 weights");
     cudaStream_t st = as_stream(stream);
-    LinArgs p{A, W, bias, C, lda, ldw, ldc, T, N, K, w_dtype, accumulate, round_a, alpha, a_bs, w_bs, bias_bs, c_bs};
+    LinArgs p{A, W, bias, C, lda, ldw, ldc, T, N, K, w_dtype, accumulate, round_a, alpha, a_bs, w_bs, bias_bs, c_bs, rows_dev};
     if (T <= kRowsMax) {
         const int e = w_dtype == SLLM_BF16 ? 8 : 4;   // elements per 16-byte weight load
         const bool vec = K % e == 0 && ldw % e == 0 && (w_bs % e) == 0 && lda % 4 == 0 && (a_bs % 4) == 0 &&
@@ -250,7 +252,7 @@ extern "C" int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32
             SLLM_LAUNCH_CHECK();
         }
         PfGemmArgs a{};
-        a.A = a16; a.W = W; a.T = T; a.N = N; a.K = K; a.tiled = 0; a.bn = 0; a.n_valid = N;
+        a.A = a16; a.W = W; a.T = T; a.N = N; a.K = K; a.tiled = 0; a.bn = 0; a.n_valid = N; a.rows_dev = rows_dev;
         if (alpha == 1.0f && ((uintptr_t)C % 16) == 0) {
             // nothing but the bias to do after the product: the GEMM's own epilogue adds it and stores (or adds) straight into C
             a.bias = bias;

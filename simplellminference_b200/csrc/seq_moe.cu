@@ -101,3 +101,162 @@ extern "C" int sllm_seq_moe_act(const float* logits, int32_t ldl, int32_t n_rout
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
 }
+
+// ---- the same layer with the tokens gathered per expert (steps of many tokens) ------------------------------------------------------------
+// Every expert gets a buffer of `cap` rows. The routing kernel gives each (token, chosen expert) pair a row of that expert's buffer
+// (an atomic counter per expert: the ORDER of rows in a buffer is whatever the hardware makes it, the numbers in a row do not depend on
+// it) and copies the token's input there; the up and down products then run per expert over the rows that are in use (the count stays on
+// the device: sllm_seq_linear's rows_dev); the combine kernel adds each token's rows, times their scores, to (identity scores) * input.
+namespace sllm {
+
+__global__ void seq_moe_route_kernel(const float* __restrict__ logits, int ldl, int n_route, int experts, int top, const float* __restrict__ correction,
+                                     const float* __restrict__ h, int ldh, int d, int32_t* __restrict__ counts, int cap, int32_t* __restrict__ sel_e,
+                                     int32_t* __restrict__ sel_pos, float* __restrict__ sel_w, float* __restrict__ ident_out, uint16_t* __restrict__ rows16,
+                                     float* __restrict__ rows32) {
+    extern __shared__ float msm[];
+    float* s_score = msm;
+    float* s_choice = msm + n_route;
+    int* s_e = reinterpret_cast<int*>(msm + 2 * n_route);   // [top] expert of the k-th choice, -1 = an expert without weights
+    int* s_pos = s_e + top;                                 // [top] its row in that expert's buffer
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    const float* z = logits + (size_t)t * ldl;
+    if (threadIdx.x < 32) {
+        float mx = -INFINITY;
+        for (int e = lane; e < n_route; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float sum = 0.0f;
+        for (int e = lane; e < n_route; e += 32) {
+            const float v = expf(z[e] - mx);
+            s_score[e] = v;
+            sum += v;
+        }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < n_route; e += 32) {
+            const float s = s_score[e] * inv;
+            s_score[e] = s;
+            s_choice[e] = s + (correction ? correction[e] : 0.0f);
+        }
+        __syncwarp();
+        float ident = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            float best = -INFINITY;
+            int arg = n_route;
+            for (int e = lane; e < n_route; e += 32) {
+                const float c = s_choice[e];
+                if (c > best) { best = c; arg = e; }
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            }
+            if (lane == 0) {
+                int e_out = -1, pos = 0;
+                float w = 0.0f;
+                if (arg < n_route) {
+                    s_choice[arg] = -INFINITY;
+                    w = s_score[arg];
+                    if (arg >= experts) ident += w;
+                    else {
+                        e_out = arg;
+                        pos = atomicAdd(counts + arg, 1);
+                        if (pos >= cap) e_out = -1;      // cannot happen with cap >= the step's tokens; never write outside the buffer
+                    }
+                }
+                s_e[k] = e_out;
+                s_pos[k] = pos;
+                sel_e[(size_t)t * top + k] = e_out;
+                sel_pos[(size_t)t * top + k] = pos;
+                sel_w[(size_t)t * top + k] = e_out >= 0 ? w : 0.0f;
+            }
+            __syncwarp();
+        }
+        if (lane == 0) ident_out[t] = ident;
+    }
+    __syncthreads();
+    const float* hr = h + (size_t)t * ldh;
+    for (int k = 0; k < top; ++k) {
+        const int e = s_e[k];
+        if (e < 0) continue;
+        const size_t row = ((size_t)e * cap + s_pos[k]) * d;
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            if (rows16) rows16[row + j] = f32_to_bf16_bits(hr[j]);
+            if (rows32) rows32[row + j] = hr[j];
+        }
+    }
+}
+
+// grid (cap, experts): rows in use only
+__global__ void seq_moe_expert_act_kernel(const float* __restrict__ up, const int32_t* __restrict__ counts, int cap, int ff, int act,
+                                          uint16_t* __restrict__ out16, float* __restrict__ out32) {
+    const int e = blockIdx.y, r = blockIdx.x;
+    if (r >= counts[e]) return;
+    const size_t row = ((size_t)e * cap + r) * ff;
+    for (int j = threadIdx.x; j < ff; j += blockDim.x) {
+        const float v = moe_act(up[row + j], act);
+        if (out16) out16[row + j] = f32_to_bf16_bits(v);
+        if (out32) out32[row + j] = v;
+    }
+}
+
+__global__ void seq_moe_combine_kernel(const float* __restrict__ down, const int32_t* __restrict__ sel_e, const int32_t* __restrict__ sel_pos,
+                                       const float* __restrict__ sel_w, int top, const float* __restrict__ ident, const float* __restrict__ h, int ldh,
+                                       int cap, int d, float* __restrict__ y, int ldy) {
+    const int t = blockIdx.x;
+    const float idw = ident[t];
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float acc = idw * h[(size_t)t * ldh + j];
+        for (int k = 0; k < top; ++k) {                      // in the order of the choice: a fixed order of the sum
+            const int e = sel_e[(size_t)t * top + k];
+            if (e >= 0) acc = fmaf(sel_w[(size_t)t * top + k], down[((size_t)e * cap + sel_pos[(size_t)t * top + k]) * d + j], acc);
+        }
+        y[(size_t)t * ldy + j] = acc;
+    }
+}
+
+}  // namespace sllm
+
+extern "C" {
+
+int sllm_seq_zero(void* p, int64_t n_bytes, sllm_stream_t stream) {
+    SLLM_REQUIRE(p && n_bytes > 0, SLLM_EINVAL, "seq_zero: bad argument");
+    SLLM_CUDA(cudaMemsetAsync(p, 0, (size_t)n_bytes, as_stream(stream)));
+    return SLLM_OK;
+}
+
+int sllm_seq_moe_route(const float* logits, int32_t ldl, int32_t n_route, int32_t experts, int32_t top, const float* correction, const float* h, int32_t ldh,
+                       int32_t d, int32_t* counts, int32_t cap, int32_t* sel_e, int32_t* sel_pos, float* sel_w, float* ident, void* rows16, float* rows32,
+                       int32_t T, sllm_stream_t stream) {
+    SLLM_REQUIRE(logits && h && counts && sel_e && sel_pos && sel_w && ident && (rows16 || rows32) && T > 0 && d > 0, SLLM_EINVAL, "seq_moe_route: bad argument");
+    SLLM_REQUIRE(experts >= 0 && n_route >= experts && n_route > 0 && top >= 1 && top <= n_route && cap >= T, SLLM_EINVAL,
+                 "seq_moe_route: %d of %d router outputs, %d experts with weights, buffers of %d rows for %d tokens", top, n_route, experts, cap, T);
+    SLLM_REQUIRE(n_route <= 4096 && top <= 1024, SLLM_ENOTSUP, "seq_moe_route: %d router outputs / top %d beyond what one CTA routes", n_route, top);
+    const size_t smem = (2 * (size_t)n_route + 2 * (size_t)top) * sizeof(float);
+    seq_moe_route_kernel<<<T, 256, smem, as_stream(stream)>>>(logits, ldl, n_route, experts, top, correction, h, ldh, d, counts, cap, sel_e, sel_pos, sel_w, ident,
+                                                               (uint16_t*)rows16, rows32);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_moe_expert_act(const float* up, const int32_t* counts, int32_t experts, int32_t cap, int32_t ff, int32_t act, void* out16, float* out32,
+                            sllm_stream_t stream) {
+    SLLM_REQUIRE(up && counts && (out16 || out32) && experts > 0 && cap > 0 && cap <= 65535 * 32 && ff > 0 && act >= 0 && act <= 2, SLLM_EINVAL, "seq_moe_expert_act: bad argument");
+    SLLM_REQUIRE(experts <= 65535, SLLM_ENOTSUP, "seq_moe_expert_act: %d experts", experts);
+    seq_moe_expert_act_kernel<<<dim3(cap, experts), 256, 0, as_stream(stream)>>>(up, counts, cap, ff, act, (uint16_t*)out16, out32);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_moe_combine(const float* down, const int32_t* sel_e, const int32_t* sel_pos, const float* sel_w, int32_t top, const float* ident, const float* h,
+                         int32_t ldh, int32_t cap, int32_t d, float* y, int32_t ldy, int32_t T, sllm_stream_t stream) {
+    SLLM_REQUIRE(down && sel_e && sel_pos && sel_w && ident && h && y && top >= 1 && T > 0 && d > 0, SLLM_EINVAL, "seq_moe_combine: bad argument");
+    seq_moe_combine_kernel<<<T, 256, 0, as_stream(stream)>>>(down, sel_e, sel_pos, sel_w, top, ident, h, ldh, cap, d, y, ldy);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+}  // extern "C"

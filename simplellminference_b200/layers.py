@@ -458,9 +458,19 @@ class ExpertsFeedForward:
     scores = softmax over ALL router outputs, the ``top`` largest (score + ``correction``) are chosen, the weights are the chosen scores
     themselves; the last ``identity`` router outputs are experts whose output is h. Computed as two wide products: every expert's up
     projection (and the router) side by side, the activation times the token's weight for that expert (zero if not chosen), and ONE down
-    product over the concatenated experts, added to (sum of the chosen identity scores) * h."""
+    product over the concatenated experts, added to (sum of the chosen identity scores) * h.
+
+    Steps of ``gather_min_tokens`` tokens and more (portions of prompts) take the gathered form instead, which multiplies a token only
+    with the experts it uses: the router alone, then a routing kernel that copies every token's input into a buffer per chosen expert,
+    per expert an up product, the activation, a down product over the rows in use (their count never leaves the device), and a kernel
+    that adds each token's rows times their scores. Both forms give the same numbers up to where the score is multiplied in."""
 
     activation = 0          # the exact (erf) gelu
+    # The gathered form trades arithmetic for launches (two products per expert): it is taken when the products it saves, at the rate the
+    # tensor-core product sustains, outweigh what its launches cost (both measured on B200: small experts are faster computed densely).
+    gather_min_tokens = 256
+    gather_launch_cost = 35e-6     # seconds per expert product
+    gather_product_rate = 7e14     # multiply-adds * 2 per second
 
     def __init__(self, cfg, w, pre, ops, device):
         self.cfg, self.ops = cfg, ops
@@ -473,12 +483,56 @@ class ExpertsFeedForward:
         self.up = FusedLinear([(w[f"{pre}e{e}.up"], None) for e in range(E)] + [(w[pre + "router"], None)], ops, device, pad_rows=8)
         self.down = FusedLinear([(torch.cat([w[f"{pre}e{e}.down"] for e in range(E)], dim=1).contiguous(), None)], ops, device)
         self.wide = E * cfg.ff
+        # the gathered form: the router as a product of its own, the down matrices one behind the other [E][d][ff]
+        self.gathers = cfg.top < self.n_route and E > 0
+        if self.gathers:
+            self.router = FusedLinear([(w[pre + "router"], None)], ops, device, pad_rows=64)    # wide enough for the tensor-core tiles
+            self.down_each = torch.stack([w[f"{pre}e{e}.down"] for e in range(E)]).contiguous()
 
     @property
     def proj(self):
         return self.up
 
+    def _forward_gathered(self, step, h, y, h16_ready=False):
+        c, ops, T, d, st = self.cfg, self.ops, step.T, self.up.K, step.st
+        E, top, ff, cap = c.experts, c.top, c.ff, step.T
+        ldl = self.router.N
+        logits = step.scratch("moe_logits", T * ldl)
+        self.router(step, h.data_ptr(), d, logits.data_ptr(), ldl, a16_ready=h16_ready)     # the bf16 rows left for the up product serve this one
+        # counts [E] | expert, row [T][top] each (int32) | score [T][top] | identity sum [T]
+        book = step.scratch("moe_book", E + 3 * T * top + T).data_ptr()
+        counts, sel_e, sel_pos, sel_w, ident = book, book + 4 * E, book + 4 * (E + T * top), book + 4 * (E + 2 * T * top), book + 4 * (E + 3 * T * top)
+        # operands of the tensor-core products are gathered as bf16 rows; shapes its tiles do not take (and the fp32 mode) gather fp32 rows
+        tc = (step.gemm_scratch(d, ff) is not None and ops.on_tensor_cores(cap, ff, d) and ops.on_tensor_cores(cap, d, ff)
+              and self.up.w.data_ptr() % 16 == 0 and self.down_each.data_ptr() % 16 == 0)
+        per = 2 if tc else 1                       # operand elements per float of scratch
+        rows = step.scratch("moe_rows", -(-E * cap * d // per)).data_ptr()
+        up_out = step.scratch("moe_up", E * cap * ff).data_ptr()
+        act = step.scratch("moe_act", -(-E * cap * ff // per)).data_ptr()
+        down_out = step.scratch("moe_down", E * cap * d).data_ptr()
+        ops.zero(counts, 4 * E, st)
+        ops.moe_route(logits.data_ptr(), ldl, self.n_route, E, top, self.correction, h, d, d, counts, cap, sel_e, sel_pos, sel_w, ident,
+                      rows if tc else None, None if tc else rows, T, st)
+        wb = self.up.w.element_size()
+        for e in range(E):
+            a = rows + e * cap * d * (2 if tc else 4)
+            ops.linear(a, d, self.up.w, d, None, up_out + 4 * e * cap * ff, ff, cap, ff, d, st, scratch=a if tc else None, a16_ready=tc, rows_dev=counts + 4 * e,
+                       w_ptr=self.up.w.data_ptr() + e * ff * d * wb)
+        ops.moe_expert_act(up_out, counts, E, cap, ff, self.activation, act if tc else None, None if tc else act, st)
+        for e in range(E):
+            a = act + e * cap * ff * (2 if tc else 4)
+            ops.linear(a, ff, self.down_each, ff, None, down_out + 4 * e * cap * d, d, cap, d, ff, st, scratch=a if tc else None, a16_ready=tc,
+                       rows_dev=counts + 4 * e, w_ptr=self.down_each.data_ptr() + e * d * ff * wb)
+        ops.moe_combine(down_out, sel_e, sel_pos, sel_w, top, ident, h, d, cap, d, y, d, T, st)
+
+    def _gathered_pays(self, T: int) -> bool:
+        c = self.cfg
+        saved = 4.0 * T * c.ff * self.up.K * (c.experts - min(c.top, c.experts)) / self.gather_product_rate
+        return self.gathers and T >= self.gather_min_tokens and saved > 2 * c.experts * self.gather_launch_cost
+
     def forward(self, step, h, y, h16_ready=False):
+        if self._gathered_pays(step.T):
+            return self._forward_gathered(step, h, y, h16_ready)
         c, T, d, N = self.cfg, step.T, self.up.K, self.up.N
         z = step.scratch("ff_z", T * N)
         self.up(step, h.data_ptr(), d, z.data_ptr(), N, a16_ready=h16_ready)

@@ -62,9 +62,12 @@ class Ops:
         self._ck(self.lib.sllm_seq_hyper_write_read(_p(x), streams, T, d, _p(mix), _p(outc), _p(y_in), _p(coef), _p(norm_w), groups, eps, _p(y_out), st))
 
     def linear(self, a_ptr, lda, w, ldw, bias, c_ptr, ldc, T, N, K, st, alpha=1.0, accumulate=False, batch=1, a_bs=0, w_bs=0, bias_bs=0,
-               c_bs=0, scratch=None, a16_ready=False):
-        self._ck(self.lib.sllm_seq_linear(a_ptr, lda, _p(w), self.w_dtype, ldw, _p(bias), c_ptr, ldc, T, N, K, alpha, int(accumulate),
-                                          self.round_a, batch, a_bs, w_bs, bias_bs, c_bs, _p(scratch) if self.tensor_cores else None, int(a16_ready), st))
+               c_bs=0, scratch=None, a16_ready=False, rows_dev=None, w_ptr=None):
+        """``w_ptr``: an address inside ``w`` to use instead of its start (one matrix of several stored back to back);
+        ``rows_dev``: device address of a row count, rows beyond it are skipped."""
+        self._ck(self.lib.sllm_seq_linear(a_ptr, lda, _p(w) if w_ptr is None else w_ptr, self.w_dtype, ldw, _p(bias), c_ptr, ldc, T, N, K, alpha, int(accumulate),
+                                          self.round_a, batch, a_bs, w_bs, bias_bs, c_bs,
+                                          (scratch if isinstance(scratch, int) else _p(scratch)) if self.tensor_cores else None, int(a16_ready), rows_dev, st))
 
     def polynorm(self, z, ldz, coef, eps, out, ldo, T, n, st):
         self._ck(self.lib.sllm_seq_polynorm(_p(z), ldz, _p(coef), eps, _p(out), ldo, T, n, st))
@@ -124,6 +127,20 @@ class Ops:
     def moe_act(self, logits_ptr, ldl, n_route, experts, top, correction, up_ptr, ldu, ff, act, h, ldh, d, out, out16, y, ldy, T, st, route_w=None):
         self._ck(self.lib.sllm_seq_moe_act(logits_ptr, ldl, n_route, experts, top, _p(correction), up_ptr, ldu, ff, act, _p(h), ldh, d, _p(out), _p(out16),
                                            _p(y), ldy, _p(route_w), T, st))
+
+    # ---- mixture of experts with the tokens gathered per expert ----
+    def zero(self, ptr, n_bytes, st):
+        self._ck(self.lib.sllm_seq_zero(ptr, n_bytes, st))
+
+    def moe_route(self, logits_ptr, ldl, n_route, experts, top, correction, h, ldh, d, counts_ptr, cap, sel_e, sel_pos, sel_w, ident, rows16, rows32, T, st):
+        self._ck(self.lib.sllm_seq_moe_route(logits_ptr, ldl, n_route, experts, top, _p(correction), _p(h), ldh, d, counts_ptr, cap, sel_e, sel_pos, sel_w, ident,
+                                             rows16, rows32, T, st))
+
+    def moe_expert_act(self, up_ptr, counts_ptr, experts, cap, ff, act, out16, out32, st):
+        self._ck(self.lib.sllm_seq_moe_expert_act(up_ptr, counts_ptr, experts, cap, ff, act, out16, out32, st))
+
+    def moe_combine(self, down_ptr, sel_e, sel_pos, sel_w, top, ident, h, ldh, cap, d, y, ldy, T, st):
+        self._ck(self.lib.sllm_seq_moe_combine(down_ptr, sel_e, sel_pos, sel_w, top, ident, _p(h), ldh, cap, d, _p(y), ldy, T, st))
 
     # ---- recurrences ----
     def conv_ring(self, b, x_ptr, ldx, channels, taps, w, ring, act, out, ldo, st):

@@ -339,6 +339,43 @@ def test_feed_forwards_alone():
                 assert _rel(O.moe_ff(h64, plain, "l0.mlp.", mlp), want) > 1e-3
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_experts_with_tokens_gathered_per_expert(dtype, monkeypatch):
+    """Steps of many tokens multiply a token only with the experts it uses (rows gathered per expert, counts kept on the device): the same
+    numbers as the restatement, and as the form that computes every expert, also when an expert gets no token at all."""
+    import torch
+
+    from simplellminference_b200 import layers
+    from simplellminference_b200.config import BF16, F32, VasosunConfig
+    from simplellminference_b200.seqops import Ops
+    rng, d, T = np.random.default_rng(14), 64, 300
+    dev, ops = torch.device("cuda"), Ops(BF16 if dtype == "bfloat16" else F32)
+    for mlp in (L.moe(experts=6, identity=2, top=3, ff=64), L.moe(experts=9, identity=0, top=1, ff=72), L.moe(experts=3, identity=5, top=2, ff=13)):
+        cfg = L.make_config([L.attention_layer(mlp=mlp)], width=d)
+        w = L.random_weights(cfg, seed=5)
+        if mlp["router"]["experts"] == 9:
+            w["l0.mlp.router"][4] = 0.0                       # an expert nobody is routed to ...
+            w["l0.mlp.correction"][4] = -5.0
+        wt = {k: torch.tensor(v, device=dev, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32) for k, v in w.items()}
+        ff = layers.ExpertsFeedForward(VasosunConfig.from_dict(cfg).layers[0].mlp, wt, "l0.mlp.", ops, dev)
+
+        def fn(step, h, states):
+            y = step.scratch("sub_out", step.T * d)
+            ff.forward(step, h, y)
+            return [y[:step.T * d].view(step.T, d)]
+        h = L.bf16_round(2 * rng.standard_normal((T, d))).astype(np.float32)
+        stub = _Stub([{"pages": [], "slots": []}], fn, ops, dev)
+        monkeypatch.setattr(layers.ExpertsFeedForward, "gather_min_tokens", 10 ** 9)
+        every = _feed(stub, h, [T])[0]
+        monkeypatch.setattr(layers.ExpertsFeedForward, "gather_min_tokens", 64)
+        monkeypatch.setattr(layers.ExpertsFeedForward, "gather_launch_cost", 0.0)
+        assert ff._gathered_pays(T) == (mlp["router"]["top"] < mlp["router"]["experts"])
+        gathered = _feed(stub, h, [T])[0]
+        want = O.moe_ff(h.astype(np.float64), _w64(w), "l0.mlp.", mlp)
+        tol = F32_TOL if dtype == "float32" else BF16_MIXER
+        assert _rel(gathered, want) < tol and _rel(every, want) < tol, (mlp, _rel(gathered, want), _rel(every, want))
+
+
 def test_pair_embedding_and_logit_cap(tmp_path):
     """The first token takes the pair table's last row, every other the hashed row of (previous token, token) — also across a cut."""
     cfg = L.make_config([L.attention_layer(mlp=None)], vocab=50, width=32, buckets=7, mul_prev=5, mul_cur=3, softcap=2.0)
