@@ -52,10 +52,10 @@ def port():
 def ref():
     from oracle import loader
     if not loader.have_ref():
-        if os.path.isdir("/root/reference"):
+        if os.path.isdir("/root/reference/source"):
             loader.build("ref")
         else:
-            pytest.skip("oracle/_ref not built and /root/reference absent")
+            pytest.skip("oracle/_ref not built and the reference's sources are not mounted")
     return loader.Ref()
 
 
