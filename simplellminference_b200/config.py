@@ -342,7 +342,7 @@ class VasosunConfig:
                 src = m.get("kv_from")
                 mixer = LatentAttentionConfig(int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"]), float(m["scale"]),
                                               RotaryConfig(int(rot["dims"]), float(rot["base"]), rot.get("scaling") or None),
-                                              WindowMask.from_dict(m.get("mask")), int(m["q_rank"]), None if src is None else int(src))
+                                              WindowMask.from_dict(m.get("mask")), int(m["q_rank"]) if m.get("q_rank") else None, None if src is None else int(src))
                 if mixer.rot.dims > mixer.rot_dim or mixer.rot.dims % 2:
                     raise ValueError(f"layer {i}: {mixer.rot.dims} rotary dimensions do not fit a rotated part of {mixer.rot_dim}")
                 if mixer.kv_from is not None:

@@ -1,6 +1,6 @@
 // csrc/seq_delta.cu — the gated delta rule over the ragged token batch, and the short causal convolution (with an activation) in front
 // of it. Per head the state S [dk][dv] (fp32, one per sequence slot) follows
-//     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+//     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q     (o of the NEW state; computed as (g S_old)^T q + u (k . q))
 // with q and k made unit vectors per head (q also times dk^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) * softplus(a + dt_bias)).
 // Everything that enters the recurrence is fp32. The columns of S are independent recurrences that share k, q, beta and g: a CTA takes
 // up to 32 columns of one head, a thread owns a piece (32 key channels) of one column in registers; the pieces of a column sit in
@@ -75,6 +75,7 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
     float* s_o = dsm + 2 * stage_floats;               // [C][CB]
     float* s_beta = s_o + C * CB;                      // [C]
     float* s_g = s_beta + C;                           // [C]
+    float* s_kq = s_g + C;                             // [C] k . q of the unit vectors
     const bool vec = p.vec;                            // 16-byte copies of q / k: dk a multiple of 4, rows 16-byte aligned
     auto issue = [&](int c0, int stage) {
         float* d_k = dsm + stage * stage_floats;
@@ -104,9 +105,9 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
             const float* vs = p.v + (size_t)(start + c0 + i / CB) * p.ldv + (size_t)h * dv;
             delta_cp4(d_v + i, col < dv ? vs + col : vs, col < dv);
         }
-        if (threadIdx.x < 2 * n) {
-            const size_t t = (size_t)(start + c0 + (threadIdx.x >> 1));
-            delta_cp4(d_l + threadIdx.x, (threadIdx.x & 1) ? p.al + t * p.lda + h : p.bl + t * p.ldb + h, true);
+        for (int i = threadIdx.x; i < 2 * n; i += blockDim.x) {
+            const size_t t = (size_t)(start + c0 + (i >> 1));
+            delta_cp4(d_l + i, (i & 1) ? p.al + t * p.lda + h : p.bl + t * p.ldb + h, true);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -129,18 +130,21 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
         float* s_q = s_k + C * RS;                     // [C][RS]
         const float* s_v = s_q + C * RS;               // [C][CB]
         const float* s_l = s_v + C * CBp;              // [C][2]
-        if (threadIdx.x < n) {
-            s_beta[threadIdx.x] = seq_sigmoid(s_l[2 * threadIdx.x]);
-            s_g[threadIdx.x] = expf(-rate * seq_softplus(s_l[2 * threadIdx.x + 1] + bias));
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            s_beta[i] = seq_sigmoid(s_l[2 * i]);
+            s_g[i] = expf(-rate * seq_softplus(s_l[2 * i + 1] + bias));
         }
         for (int tok = warp; tok < n; tok += nwarps) {                             // unit vectors: a warp per token
-            float sk = 0.0f, sq = 0.0f;
+            float sk = 0.0f, sq = 0.0f, skq = 0.0f;
             for (int kr = lane; kr < PP * kDeltaKP; kr += 32) {
                 const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + kr % kDeltaKP;
                 sk = fmaf(s_k[at], s_k[at], sk);
                 sq = fmaf(s_q[at], s_q[at], sq);
+                skq = fmaf(s_k[at], s_q[at], skq);
             }
             const float ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps), iq = p.qscale / sqrtf(warp_sum(sq) + p.unit_eps);
+            skq = warp_sum(skq);
+            if (lane == 0) s_kq[tok] = (skq * ik) * iq;
             for (int kr = lane; kr < PP * kDeltaKP; kr += 32) {
                 const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + kr % kDeltaKP;
                 s_k[at] *= ik;
@@ -148,39 +152,35 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
             }
         }
         __syncthreads();
+        // One token: with D = g S the rule reads u = beta (v - D^T k), S' = D + k u^T, o = S'^T q = D^T q + u (k . q). Both products with the
+        // OLD state run side by side (one pass over the piece, ONE round of shuffles for the two sums), and k . q is a number per token:
+        // the serial chain of a token holds one reduction instead of two.
         for (int i = 0; i < n; ++i) {
-            const float g = s_g[i], beta = s_beta[i];
+            const float g = s_g[i], beta = s_beta[i], kq = s_kq[i];
             const float4* kk = reinterpret_cast<const float4*>(s_k + i * RS + part * kDeltaRS);
             const float4* qq = reinterpret_cast<const float4*>(s_q + i * RS + part * kDeltaRS);
             float kr[kDeltaKP];
-            float d4[4] = {0.0f, 0.0f, 0.0f, 0.0f};          // four running sums: no chain of 32 dependent multiply-adds
+            float d4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, e4[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // four running sums each: no long chain of dependent multiply-adds
 #pragma unroll
             for (int x = 0; x < kDeltaKP; x += 4) {
-                const float4 kv = kk[x >> 2];
+                const float4 kv = kk[x >> 2], qv = qq[x >> 2];
+                const float qr[4] = {qv.x, qv.y, qv.z, qv.w};
                 kr[x] = kv.x; kr[x + 1] = kv.y; kr[x + 2] = kv.z; kr[x + 3] = kv.w;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    S[x + e] *= g;
                     d4[e] = fmaf(S[x + e], kr[x + e], d4[e]);
+                    e4[e] = fmaf(S[x + e], qr[e], e4[e]);
                 }
             }
-            float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
-            for (int o = PP >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const float u = beta * ((live ? s_v[i * CB + jl] : 0.0f) - dot);
-            float o4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int x = 0; x < kDeltaKP; x += 4) {
-                const float4 qv = qq[x >> 2];
-                const float qr[4] = {qv.x, qv.y, qv.z, qv.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    S[x + e] = fmaf(kr[x + e], u, S[x + e]);
-                    o4[e] = fmaf(S[x + e], qr[e], o4[e]);
-                }
+            float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]), dq = (e4[0] + e4[1]) + (e4[2] + e4[3]);
+            for (int o = PP >> 1; o > 0; o >>= 1) {
+                dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                dq += __shfl_xor_sync(0xffffffffu, dq, o);
             }
-            float out = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-            for (int o = PP >> 1; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-            if (live && part == 0) s_o[i * CB + jl] = out;
+            const float u = beta * ((live ? s_v[i * CB + jl] : 0.0f) - g * dot);
+            if (live && part == 0) s_o[i * CB + jl] = fmaf(u, kq, g * dq);
+#pragma unroll
+            for (int x = 0; x < kDeltaKP; ++x) S[x] = fmaf(kr[x], u, g * S[x]);
         }
         __syncthreads();
         for (int i = threadIdx.x; i < n * CB; i += blockDim.x) {
@@ -244,17 +244,28 @@ int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, co
     if (tune_cb > 0) CB = std::min(dv, tune_cb);
     const int blocks = (dv + CB - 1) / CB;
     const int threads = (CB * PP + 31) / 32 * 32;
-    const int per_tok = 2 * (2 * PP * RSh + ((CB + 3) & ~3) + 4) + CB + 2;      // two stages of inputs, one of outputs
-    const int chunk = std::max(1, std::min(16, 11264 / per_tok));
+    const int per_tok = 2 * (2 * PP * RSh + ((CB + 3) & ~3) + 4) + CB + 3;      // two stages of inputs, one of outputs
+    // tokens per stage: every stage costs a round trip to memory and three barriers whatever its size (measured: 12 tokens per stage spent
+    // most of the time there), so portions use up to 160 KB of shared memory; steps of single tokens keep the stages small
+    static const int tune_chunk = getenv("SLLM_DELTA_CHUNK") ? atoi(getenv("SLLM_DELTA_CHUNK")) : 0;
+    const int longest = b->T - b->nseg + 1;                                   // no portion is longer than this
+    int chunk = std::max(1, std::min(std::min(64, longest), 40960 / per_tok));
+    if (tune_chunk > 0) chunk = std::max(1, std::min(tune_chunk, 50000 / per_tok));
     const size_t smem = (size_t)chunk * per_tok * sizeof(float);
-    SLLM_REQUIRE(smem <= 48 * 1024, SLLM_ENOTSUP, "seq_delta_rule: one token of a %d x %d head needs %zu bytes of shared memory", dk, dv, smem);
+    SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes() - 2048, SLLM_ENOTSUP, "seq_delta_rule: one token of a %d x %d head needs %zu bytes of shared memory", dk, dv, smem);
     const int vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0;
     DeltaArgs p{*b, q, k, v, ldq, ldk, ldv, beta_logit, step_logit, ldb, lda, A_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale, state, o, ldo,
                 conv_x, ldx, channels, taps, ring, chunk, PP, CB, vec};
-    if (KP == 8) seq_delta_kernel<8, 1024><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
-    else if (KP == 16) seq_delta_kernel<16, 512><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
-    else if (threads <= 256) seq_delta_kernel<32, 256><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
-    else seq_delta_kernel<32, 1024><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);
+#define SLLM_DELTA_LAUNCH(KPV, MAXT)                                                                                                              \
+    do {                                                                                                                                          \
+        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_delta_kernel<KPV, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        seq_delta_kernel<KPV, MAXT><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);                                       \
+    } while (0)
+    if (KP == 8) SLLM_DELTA_LAUNCH(8, 1024);
+    else if (KP == 16) SLLM_DELTA_LAUNCH(16, 512);
+    else if (threads <= 256) SLLM_DELTA_LAUNCH(32, 256);
+    else SLLM_DELTA_LAUNCH(32, 1024);
+#undef SLLM_DELTA_LAUNCH
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

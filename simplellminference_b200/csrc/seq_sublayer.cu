@@ -129,7 +129,13 @@ __global__ void seq_seam_sum_kernel(SeamArgs p, float* __restrict__ scale) {
     if (threadIdx.x == 0) scale[t] = p.pre_g / sqrtf(ss / (float)d + p.eps);
 }
 
-__global__ void seq_seam_conv_kernel(SeamArgs p, const float* __restrict__ scale) {
+constexpr int kSeamMaxTaps = 64;
+
+// The rows a token's convolution reads are found once per CTA (the step's own rows with their scales, or ring rows), then the channels
+// are walked four at a time with 16-byte loads where the row length allows.
+__global__ void seq_seam_conv_kernel(SeamArgs p, const float* __restrict__ scale, int vec) {
+    __shared__ const float* s_src[kSeamMaxTaps];   // [back] row that lies `back` positions before the token, NULL = before the sequence's start
+    __shared__ float s_mul[kSeamMaxTaps];
     const sllm_seq_batch& b = p.b;
     const int t = blockIdx.x, d = p.d, slot = b.tok_slot[t], pos = b.tok_pos[t], taps = p.taps;
     const float* x = p.y ? p.x_out : p.x_in;             // the stream after the sum
@@ -137,16 +143,56 @@ __global__ void seq_seam_conv_kernel(SeamArgs p, const float* __restrict__ scale
     const bool keep = seam_is_last(b, t, slot, taps - 1);
     float* fdst = flush ? p.flush_ring + ((size_t)slot * (p.flush_taps - 1) + pos % (p.flush_taps - 1)) * d : nullptr;
     const size_t r = (size_t)t * d;
-    const float own = scale[t];
+    if ((int)threadIdx.x < taps) {
+        const int back = threadIdx.x;
+        const float* src = nullptr;
+        float mul = 1.0f;
+        if (pos - back >= 0) {
+            if (back == 0 || (t - back >= 0 && b.tok_slot[t - back] == slot)) {
+                src = x + r - (size_t)back * d;
+                mul = scale[t - back];
+            } else {
+                src = p.ring + ((size_t)slot * (taps - 1) + (pos - back) % (taps - 1)) * d;
+            }
+        }
+        s_src[back] = src;
+        s_mul[back] = mul;
+    }
+    __syncthreads();
+    const float own = s_mul[0];
+    if (vec) {
+        for (int j = (blockIdx.y * blockDim.x + threadIdx.x) * 4; j < d; j += gridDim.y * blockDim.x * 4) {
+            if (flush) *reinterpret_cast<float4*>(fdst + j) = *reinterpret_cast<const float4*>(p.stash + r + j);
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int back = taps - 1; back >= 1; --back) {
+                const float* src = s_src[back];
+                if (!src) continue;
+                const float4 v = *reinterpret_cast<const float4*>(src + j);
+                const float m = s_mul[back];
+                const float n4[4] = {v.x * m, v.y * m, v.z * m, v.w * m};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[e] = fmaf(p.conv_w[(size_t)(j + e) * taps + taps - 1 - back], n4[e], acc[e]);
+            }
+            const float4 v = *reinterpret_cast<const float4*>(x + r + j);
+            const float n4[4] = {v.x * own, v.y * own, v.z * own, v.w * own};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(p.conv_w[(size_t)(j + e) * taps + taps - 1], n4[e], acc[e]) + n4[e];
+            *reinterpret_cast<float4*>(p.h + r + j) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            if (p.h16) {
+                const uint2 packed = make_uint2((uint32_t)f32_to_bf16_bits(acc[0]) | ((uint32_t)f32_to_bf16_bits(acc[1]) << 16),
+                                                (uint32_t)f32_to_bf16_bits(acc[2]) | ((uint32_t)f32_to_bf16_bits(acc[3]) << 16));
+                *reinterpret_cast<uint2*>(p.h16 + r + j) = packed;
+            }
+            if (keep) *reinterpret_cast<float4*>(p.stash + r + j) = make_float4(n4[0], n4[1], n4[2], n4[3]);
+        }
+        return;
+    }
     for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < d; j += gridDim.y * blockDim.x) {
         if (flush) fdst[j] = p.stash[r + j];
         float acc = 0.0f;
         for (int back = taps - 1; back >= 1; --back) {
-            if (pos - back < 0) continue;
-            const bool here = t - back >= 0 && b.tok_slot[t - back] == slot;
-            const float n = here ? x[r - (size_t)back * d + j] * scale[t - back]
-                                 : p.ring[((size_t)slot * (taps - 1) + (pos - back) % (taps - 1)) * d + j];
-            acc = fmaf(p.conv_w[(size_t)j * taps + taps - 1 - back], n, acc);
+            const float* src = s_src[back];
+            if (src) acc = fmaf(p.conv_w[(size_t)j * taps + taps - 1 - back], src[j] * s_mul[back], acc);
         }
         const float n = x[r + j] * own;
         acc = fmaf(p.conv_w[(size_t)j * taps + taps - 1], n, acc) + n;
@@ -166,7 +212,7 @@ extern "C" int sllm_seq_seam(const sllm_seq_batch* b, const float* x_in, float* 
     SLLM_REQUIRE(b && b->T > 0 && b->tok_slot && b->tok_pos, SLLM_EINVAL, "seq_seam: incomplete batch description");
     SLLM_REQUIRE(x_in && d > 0 && (!y || (x_out && x_out != x_in)), SLLM_EINVAL, "seq_seam: the residual sum needs a second buffer for x");
     SLLM_REQUIRE(!has_pre || h, SLLM_EINVAL, "seq_seam: no output for the normed rows");
-    SLLM_REQUIRE(!conv_w || (taps >= 1 && taps <= 64 && (taps == 1 || (ring && stash))), SLLM_EINVAL, "seq_seam: a convolution needs its ring and a stash");
+    SLLM_REQUIRE(!conv_w || (taps >= 1 && taps <= kSeamMaxTaps && (taps == 1 || (ring && stash))), SLLM_EINVAL, "seq_seam: a convolution (1..%d taps) needs its ring and a stash", kSeamMaxTaps);
     SLLM_REQUIRE(!flush_ring || (flush_taps >= 2 && stash), SLLM_EINVAL, "seq_seam: nothing to flush from");
     if (conv_w && taps == 1) ring = nullptr;
     const size_t smem = 2 * (size_t)d * sizeof(float);
@@ -176,7 +222,10 @@ extern "C" int sllm_seq_seam(const sllm_seq_batch* b, const float* x_in, float* 
     const int threads = b->T >= 64 ? (d >= 2048 ? 256 : 128) : std::min(1024, std::max(128, (d + 31) / 32 * 32));
     if (scales && has_pre && conv_w && b->T >= 64 && b->T <= 65535) {       // many tokens: two launches, every row normed once
         seq_seam_sum_kernel<<<b->T, threads, smem / 2, as_stream(stream)>>>(p, scales);
-        seq_seam_conv_kernel<<<dim3(b->T, std::max(1, std::min(8, d / 1024))), 256, 0, as_stream(stream)>>>(p, scales);
+        auto aligned = [](const void* q) { return q == nullptr || ((uintptr_t)q % 16) == 0; };
+        const int vec = d % 4 == 0 && aligned(x_in) && aligned(x_out) && aligned(ring) && aligned(h) && aligned(stash) && aligned(flush_ring) &&
+                        (h16 == nullptr || ((uintptr_t)h16 % 8) == 0);
+        seq_seam_conv_kernel<<<dim3(b->T, std::max(1, std::min(4, d / 4096))), 256, 0, as_stream(stream)>>>(p, scales, vec);
         g_launches += 2;
         SLLM_LAUNCH_CHECK();
         return SLLM_OK;
