@@ -438,6 +438,12 @@ int sllm_seq_hyper_write_read(float* x, int32_t streams, int32_t T, int32_t d, c
 int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32_t w_dtype, int32_t ldw, const float* bias, float* C, int32_t ldc,
                     int32_t T, int32_t N, int32_t K, float alpha, int32_t accumulate, int32_t round_a, int32_t batch, int64_t a_bs,
                     int64_t w_bs, int64_t bias_bs, int64_t c_bs, void* a16, int32_t a16_ready, const int32_t* rows_dev, sllm_stream_t stream);
+/* `batch` products of ONE activation row each, every one with a matrix chosen on the device: C[b] = A[b / a_div] . W[w_index[b]]^T,
+ * matrices w_bs elements apart in W, rows a_bs / c_bs apart in A / C; w_index[b] < 0 = no matrix (C[b] = 0). The weight-streaming body
+ * of sllm_seq_linear: each product reads only its own matrix (a mixture of experts at decode sizes). */
+int sllm_seq_linear_indexed(const float* A, int32_t lda, int64_t a_bs, int32_t a_div, const void* W, int32_t w_dtype, int32_t ldw, int64_t w_bs,
+                            const int32_t* w_index, float* C, int32_t ldc, int64_t c_bs, int32_t batch, int32_t N, int32_t K, int32_t round_a,
+                            sllm_stream_t stream);
 /* 1 when sllm_seq_linear with a bf16 scratch sends this shape to the tensor cores (the weights must also be 16-byte aligned) */
 int sllm_seq_linear_on_tensor_cores(int32_t T, int32_t N, int32_t K, int32_t w_dtype, int32_t ldw, int32_t batch, int32_t round_a);
 /* PolyNorm: out = c0*N(z) + c1*N(z^2) + c2*N(z^3) + c3, powers element-wise, N(v) = v / sqrt(mean(v^2) + eps) over a row; coef: 4 floats */
@@ -547,6 +553,9 @@ int sllm_seq_moe_expert_act(const float* up, const int32_t* counts, int32_t expe
                             float* out32, sllm_stream_t stream);
 int sllm_seq_moe_combine(const float* down, const int32_t* sel_e, const int32_t* sel_pos, const float* sel_w, int32_t top, const float* ident,
                          const float* h, int32_t ldh, int32_t cap, int32_t d, float* y, int32_t ldy, int32_t T, sllm_stream_t stream);
+/* x <- act(x) over n floats (act as in sllm_seq_moe_act). With counts, rows16 and rows32 all NULL sllm_seq_moe_route only routes: nothing is
+ * gathered and sel_pos of pair (t, k) is t * top + k. */
+int sllm_seq_act(float* x, int64_t n, int32_t act, sllm_stream_t stream);
 /* n_bytes of zeros at p, in stream order */
 int sllm_seq_zero(void* p, int64_t n_bytes, sllm_stream_t stream);
 /* y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + bias per row (bias NULL = none); y16 (or NULL): the same rows once more, rounded

@@ -140,6 +140,8 @@ SIGNATURES.update({
     "sllm_seq_moe_expert_act": (C.c_int, [_P, _P, _I, _I, _I, _I, _P, _P, _P]),
     "sllm_seq_moe_combine": (C.c_int, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _I, _I, _P]),
     "sllm_seq_zero": (C.c_int, [_P, _L, _P]),
+    "sllm_seq_act": (C.c_int, [_P, _L, _I, _P]),
+    "sllm_seq_linear_indexed": (C.c_int, [_P, _I, _L, _I, _P, _I, _I, _L, _P, _P, _I, _L, _I, _I, _I, _I, _P]),
     "sllm_seq_linear_on_tensor_cores": (C.c_int, [_I, _I, _I, _I, _I, _I, _I]),
     "sllm_seq_polynorm": (C.c_int, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
     "sllm_seq_gather_rows": (C.c_int, [_P, _I, _P, _I, _I, _P, _P]),

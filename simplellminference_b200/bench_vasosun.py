@@ -4,8 +4,8 @@ per second of one whole prompt, and decoded tokens per second of 1 and 4 request
 Used by ``bench.py --vasosun``; prints one JSON object per model and size.
 
 Timing and roofline fractions as in ``bench_hybrid`` (CUDA events on the launching stream, 3 warm-ups, medians). The algorithmic work of
-a mixture-of-experts layer is that of the experts a token USES (on average top * experts / (experts + identity) of them); the
-implementation computes every expert for every token, and the fractions show it."""
+a mixture-of-experts layer is that of the experts a token USES (on average top * experts / (experts + identity) of them); where the
+implementation computes every expert for every token (small experts, steps of a few tokens) the "executed" fractions show it."""
 from __future__ import annotations
 
 import json
@@ -114,6 +114,7 @@ def bench_vasosun(name: str, hbm_gbs: float, tflops: float) -> dict:
     import torch
 
     from .config import BF16, VasosunConfig
+    from .layers import ExpertsFeedForward
     from .models.vasosun import VasosunModel
     from .seqengine import SequenceEngine
     from .seqops import Ops
@@ -166,8 +167,11 @@ def bench_vasosun(name: str, hbm_gbs: float, tflops: float) -> dict:
         out[f"decode{n}_tokens_per_sec"] = round(n / ms * 1e3, 1)
         # one request reads the experts it uses; four requests together touch most of them
         weights = used if n == 1 else total
+        # what the step really streams: only the chosen experts where the expert layers take the indexed form at this batch size
+        experts = [sub.body for subs in model.layers for sub in subs if isinstance(sub.body, ExpertsFeedForward)]
+        executed = used if (n == 1 and experts and all(f._indexed_pays(n) for f in experts)) else total
         out[f"decode{n}_fraction_of_measured_hbm"] = round((2.0 * weights + n * state_bytes) / (ms * 1e-3) / (hbm_gbs * 1e9), 3)
-        out[f"decode{n}_fraction_of_measured_hbm_executed"] = round((2.0 * total + n * state_bytes) / (ms * 1e-3) / (hbm_gbs * 1e9), 3)
+        out[f"decode{n}_fraction_of_measured_hbm_executed"] = round((2.0 * executed + n * state_bytes) / (ms * 1e-3) / (hbm_gbs * 1e9), 3)
         for s in slots:
             eng.release(s)
     out["graph_replays"] = eng.graph_replays

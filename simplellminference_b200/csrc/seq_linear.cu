@@ -20,6 +20,8 @@ struct LinArgs {
     float alpha;
     long long a_bs, w_bs, bias_bs, c_bs;
     const int32_t* rows_dev;   // device memory or NULL: rows from *rows_dev on are not computed (tile body and tensor cores)
+    const int32_t* w_index;    // rows body, device memory or NULL: product b of the batch uses matrix w_index[b] (W + w_index[b] * w_bs); -1 = no matrix, zeros
+    int a_div;                 // rows body: product b reads the activations of batch element b / a_div (0 or 1: its own)
 };
 
 constexpr int kRowsMax = 8;
@@ -37,7 +39,8 @@ template <int WD>
 __global__ void __launch_bounds__(256, SLLM_ROWS_MINB) seq_linear_rows_kernel(LinArgs p, int vec, int wpr) {
     __shared__ float part_sum[8][kRowsMax];
     const int b = blockIdx.y;
-    const float* A = p.A + (size_t)b * p.a_bs;
+    const int wb = p.w_index ? p.w_index[b] : b;             // which matrix of W; negative: none (the outputs are zeros)
+    const float* A = p.A + (size_t)(p.a_div > 1 ? b / p.a_div : b) * p.a_bs;
     const float* bias = p.bias ? p.bias + (size_t)b * p.bias_bs : nullptr;
     float* C = p.C + (size_t)b * p.c_bs;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -48,9 +51,9 @@ __global__ void __launch_bounds__(256, SLLM_ROWS_MINB) seq_linear_rows_kernel(Li
     float acc[kRowsMax];
 #pragma unroll
     for (int t = 0; t < kRowsMax; ++t) acc[t] = 0.0f;
-    if (n < p.N) {
+    if (n < p.N && wb >= 0) {
         if (vec) {
-            const uint8_t* w = reinterpret_cast<const uint8_t*>(p.W) + ((size_t)b * p.w_bs + (size_t)n * p.ldw) * (16 / E);
+            const uint8_t* w = reinterpret_cast<const uint8_t*>(p.W) + ((size_t)wb * p.w_bs + (size_t)n * p.ldw) * (16 / E);
             constexpr int kStep = kInFlight * 32 * E;
             auto load = [&](uint4 (&u)[kInFlight], int k0) {
 #pragma unroll
@@ -100,7 +103,7 @@ __global__ void __launch_bounds__(256, SLLM_ROWS_MINB) seq_linear_rows_kernel(Li
             }
         } else {
             for (int k = k_lo + lane; k < k_hi; k += 32) {
-                const size_t wi = (size_t)b * p.w_bs + (size_t)n * p.ldw + k;
+                const size_t wi = (size_t)wb * p.w_bs + (size_t)n * p.ldw + k;
                 const float wv = WD == SLLM_BF16 ? seq_ld(reinterpret_cast<const uint16_t*>(p.W), wi) : reinterpret_cast<const float*>(p.W)[wi];
 #pragma unroll
                 for (int t = 0; t < kRowsMax; ++t)
@@ -216,6 +219,33 @@ __global__ void seq_linear_epilogue_kernel(const float* __restrict__ P, const fl
 
 using namespace sllm;
 
+// the rows body: up to 8 activation rows per product, `batch` products
+static int launch_rows(const sllm::LinArgs& p, int batch, cudaStream_t st) {
+    using namespace sllm;
+    const int e = p.w_dtype == SLLM_BF16 ? 8 : 4;   // elements per 16-byte weight load
+    const bool vec = p.K % e == 0 && p.ldw % e == 0 && (p.w_bs % e) == 0 && p.lda % 4 == 0 && (p.a_bs % 4) == 0 && ((uintptr_t)p.W % 16) == 0 &&
+                     ((uintptr_t)p.A % 16) == 0;
+    int wpr = 1;   // warps per output column: enough CTAs for ~4 per SM, and no warp with less than 256 weights
+    while (wpr < 8 && (long long)p.N * batch * wpr / 8 < 4LL * sm_count() && p.K / (2 * wpr) >= 256) wpr *= 2;
+    dim3 grid(((long long)p.N * wpr + 7) / 8, batch);
+    if (p.w_dtype == SLLM_BF16) seq_linear_rows_kernel<SLLM_BF16><<<grid, 256, 0, st>>>(p, vec, wpr);
+    else seq_linear_rows_kernel<SLLM_F32><<<grid, 256, 0, st>>>(p, vec, wpr);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+extern "C" int sllm_seq_linear_indexed(const float* A, int32_t lda, int64_t a_bs, int32_t a_div, const void* W, int32_t w_dtype, int32_t ldw, int64_t w_bs,
+                                       const int32_t* w_index, float* C, int32_t ldc, int64_t c_bs, int32_t batch, int32_t N, int32_t K, int32_t round_a,
+                                       sllm_stream_t stream) {
+    using namespace sllm;
+    SLLM_REQUIRE(A && W && C && w_index && batch > 0 && batch <= 65535 && N > 0 && K > 0 && a_div >= 1, SLLM_EINVAL, "seq_linear_indexed: bad argument");
+    SLLM_REQUIRE(lda >= K && ldw >= K && ldc >= N, SLLM_EINVAL, "seq_linear_indexed: row strides shorter than the rows");
+    SLLM_REQUIRE(w_dtype == SLLM_F32 || w_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_linear_indexed: fp32 or bf16 weights");
+    LinArgs p{A, W, nullptr, C, lda, ldw, ldc, 1, N, K, w_dtype, 0, round_a, 1.0f, a_bs, w_bs, 0, c_bs, nullptr, w_index, a_div};
+    return launch_rows(p, batch, as_stream(stream));
+}
+
 extern "C" int sllm_seq_linear_on_tensor_cores(int32_t T, int32_t N, int32_t K, int32_t w_dtype, int32_t ldw, int32_t batch, int32_t round_a) {
     // bf16 weights and operands, rows that TMA can address (16-byte multiples) and enough work to fill tiles
     return w_dtype == SLLM_BF16 && batch == 1 && round_a && T >= 64 && N >= 64 && K >= 64 && K % 8 == 0 && ldw == K && N % 4 == 0;
@@ -228,20 +258,8 @@ extern "C" int sllm_seq_linear(const float* A, int32_t lda, const void* W, int32
     SLLM_REQUIRE(lda >= K && ldw >= K && ldc >= N, SLLM_EINVAL, "seq_linear: row strides shorter than the rows");
     SLLM_REQUIRE(w_dtype == SLLM_F32 || w_dtype == SLLM_BF16, SLLM_ENOTSUP, "seq_linear: fp32 or bf16 weights");
     cudaStream_t st = as_stream(stream);
-    LinArgs p{A, W, bias, C, lda, ldw, ldc, T, N, K, w_dtype, accumulate, round_a, alpha, a_bs, w_bs, bias_bs, c_bs, rows_dev};
-    if (T <= kRowsMax) {
-        const int e = w_dtype == SLLM_BF16 ? 8 : 4;   // elements per 16-byte weight load
-        const bool vec = K % e == 0 && ldw % e == 0 && (w_bs % e) == 0 && lda % 4 == 0 && (a_bs % 4) == 0 &&
-                         ((uintptr_t)W % 16) == 0 && ((uintptr_t)A % 16) == 0;
-        int wpr = 1;   // warps per output column: enough CTAs for ~4 per SM, and no warp with less than 256 weights
-        while (wpr < 8 && (long long)N * batch * wpr / 8 < 4LL * sm_count() && K / (2 * wpr) >= 256) wpr *= 2;
-        dim3 grid(((long long)N * wpr + 7) / 8, batch);
-        if (w_dtype == SLLM_BF16) seq_linear_rows_kernel<SLLM_BF16><<<grid, 256, 0, st>>>(p, vec, wpr);
-        else seq_linear_rows_kernel<SLLM_F32><<<grid, 256, 0, st>>>(p, vec, wpr);
-        ++g_launches;
-        SLLM_LAUNCH_CHECK();
-        return SLLM_OK;
-    }
+    LinArgs p{A, W, bias, C, lda, ldw, ldc, T, N, K, w_dtype, accumulate, round_a, alpha, a_bs, w_bs, bias_bs, c_bs, rows_dev, nullptr, 0};
+    if (T <= kRowsMax) return launch_rows(p, batch, st);
     // tensor cores: bf16 weights, a dense bf16 copy of A, rows that TMA can address (16-byte multiples) and enough work to fill tiles
     if (a16 && sllm_seq_linear_on_tensor_cores(T, N, K, w_dtype, ldw, batch, round_a) && ((uintptr_t)W % 16) == 0) {
         static PfCache* cache = pf_cache_create();

@@ -160,8 +160,9 @@ __global__ void seq_moe_route_kernel(const float* __restrict__ logits, int ldl, 
                     if (arg >= experts) ident += w;
                     else {
                         e_out = arg;
-                        pos = atomicAdd(counts + arg, 1);
-                        if (pos >= cap) e_out = -1;      // cannot happen with cap >= the step's tokens; never write outside the buffer
+                        // without counters nothing is gathered: the pair keeps its own number, (token, choice) in order
+                        pos = counts ? atomicAdd(counts + arg, 1) : t * top + k;
+                        if (counts && pos >= cap) e_out = -1;      // cannot happen with cap >= the step's tokens; never write outside the buffer
                     }
                 }
                 s_e[k] = e_out;
@@ -175,6 +176,7 @@ __global__ void seq_moe_route_kernel(const float* __restrict__ logits, int ldl, 
         if (lane == 0) ident_out[t] = ident;
     }
     __syncthreads();
+    if (!rows16 && !rows32) return;
     const float* hr = h + (size_t)t * ldh;
     for (int k = 0; k < top; ++k) {
         const int e = s_e[k];
@@ -185,6 +187,11 @@ __global__ void seq_moe_route_kernel(const float* __restrict__ logits, int ldl, 
             if (rows32) rows32[row + j] = hr[j];
         }
     }
+}
+
+// x <- act(x) over n floats
+__global__ void seq_act_kernel(float* __restrict__ x, size_t n, int act) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] = moe_act(x[i], act);
 }
 
 // grid (cap, experts): rows in use only
@@ -219,6 +226,14 @@ __global__ void seq_moe_combine_kernel(const float* __restrict__ down, const int
 
 extern "C" {
 
+int sllm_seq_act(float* x, int64_t n, int32_t act, sllm_stream_t stream) {
+    SLLM_REQUIRE(x && n > 0 && act >= 0 && act <= 2, SLLM_EINVAL, "seq_act: bad argument");
+    seq_act_kernel<<<(int)std::min<size_t>(((size_t)n + 255) / 256, (size_t)sm_count() * 8), 256, 0, as_stream(stream)>>>(x, (size_t)n, act);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
 int sllm_seq_zero(void* p, int64_t n_bytes, sllm_stream_t stream) {
     SLLM_REQUIRE(p && n_bytes > 0, SLLM_EINVAL, "seq_zero: bad argument");
     SLLM_CUDA(cudaMemsetAsync(p, 0, (size_t)n_bytes, as_stream(stream)));
@@ -228,7 +243,8 @@ int sllm_seq_zero(void* p, int64_t n_bytes, sllm_stream_t stream) {
 int sllm_seq_moe_route(const float* logits, int32_t ldl, int32_t n_route, int32_t experts, int32_t top, const float* correction, const float* h, int32_t ldh,
                        int32_t d, int32_t* counts, int32_t cap, int32_t* sel_e, int32_t* sel_pos, float* sel_w, float* ident, void* rows16, float* rows32,
                        int32_t T, sllm_stream_t stream) {
-    SLLM_REQUIRE(logits && h && counts && sel_e && sel_pos && sel_w && ident && (rows16 || rows32) && T > 0 && d > 0, SLLM_EINVAL, "seq_moe_route: bad argument");
+    SLLM_REQUIRE(logits && h && sel_e && sel_pos && sel_w && ident && T > 0 && d > 0, SLLM_EINVAL, "seq_moe_route: bad argument");
+    SLLM_REQUIRE((counts != nullptr) == (rows16 || rows32), SLLM_EINVAL, "seq_moe_route: counters and row buffers come together");
     SLLM_REQUIRE(experts >= 0 && n_route >= experts && n_route > 0 && top >= 1 && top <= n_route && cap >= T, SLLM_EINVAL,
                  "seq_moe_route: %d of %d router outputs, %d experts with weights, buffers of %d rows for %d tokens", top, n_route, experts, cap, T);
     SLLM_REQUIRE(n_route <= 4096 && top <= 1024, SLLM_ENOTSUP, "seq_moe_route: %d router outputs / top %d beyond what one CTA routes", n_route, top);

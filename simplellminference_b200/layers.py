@@ -463,7 +463,9 @@ class ExpertsFeedForward:
     Steps of ``gather_min_tokens`` tokens and more (portions of prompts) take the gathered form instead, which multiplies a token only
     with the experts it uses: the router alone, then a routing kernel that copies every token's input into a buffer per chosen expert,
     per expert an up product, the activation, a down product over the rows in use (their count never leaves the device), and a kernel
-    that adds each token's rows times their scores. Both forms give the same numbers up to where the score is multiplied in."""
+    that adds each token's rows times their scores. Steps of one or two tokens (decoding) whose experts are large take the indexed
+    form: the router, a routing kernel, and ONE up and ONE down launch in which every (token, choice) pair streams only its own expert's
+    matrix, chosen on the device. All forms give the same numbers up to where the score is multiplied in."""
 
     activation = 0          # the exact (erf) gelu
     # The gathered form trades arithmetic for launches (two products per expert): it is taken when the products it saves, at the rate the
@@ -471,6 +473,9 @@ class ExpertsFeedForward:
     gather_min_tokens = 256
     gather_launch_cost = 35e-6     # seconds per expert product
     gather_product_rate = 7e14     # multiply-adds * 2 per second
+    # The indexed form reads (pairs / experts) of the expert bytes at the price of three more launches per layer
+    index_launch_cost = 12e-6      # seconds for the three extra launches of a step replayed as a graph
+    index_stream_rate = 5e12       # bytes per second the weight-streaming body sustains
 
     def __init__(self, cfg, w, pre, ops, device):
         self.cfg, self.ops = cfg, ops
@@ -530,9 +535,34 @@ class ExpertsFeedForward:
         saved = 4.0 * T * c.ff * self.up.K * (c.experts - min(c.top, c.experts)) / self.gather_product_rate
         return self.gathers and T >= self.gather_min_tokens and saved > 2 * c.experts * self.gather_launch_cost
 
+    def _indexed_pays(self, T: int) -> bool:
+        c = self.cfg
+        pairs = T * c.top
+        saved = (c.experts - pairs) * 2.0 * c.ff * self.up.K * self.up.w.element_size() / self.index_stream_rate
+        return self.gathers and T <= 8 and pairs < c.experts and saved > self.index_launch_cost
+
+    def _forward_indexed(self, step, h, y):
+        c, ops, T, d, st = self.cfg, self.ops, step.T, self.up.K, step.st
+        E, top, ff = c.experts, c.top, c.ff
+        pairs, ldl = T * top, self.router.N
+        logits = step.scratch("moe_logits", T * ldl)
+        self.router(step, h.data_ptr(), d, logits.data_ptr(), ldl)
+        book = step.scratch("moe_book", E + 3 * pairs + T).data_ptr()       # as in the gathered form; the counters stay unused
+        sel_e, sel_pos, sel_w, ident = book + 4 * E, book + 4 * (E + pairs), book + 4 * (E + 2 * pairs), book + 4 * (E + 3 * pairs)
+        ops.moe_route(logits.data_ptr(), ldl, self.n_route, E, top, self.correction, h, d, d, None, T, sel_e, sel_pos, sel_w, ident, None, None, T, st)
+        up_out = step.scratch("moe_up", pairs * ff).data_ptr()
+        down_out = step.scratch("moe_down", pairs * d).data_ptr()
+        ops.linear_indexed(h.data_ptr(), d, d, top, self.up.w, d, ff * d, sel_e, up_out, ff, ff, pairs, ff, d, st)
+        ops.act(up_out, pairs * ff, self.activation, st)
+        ops.linear_indexed(up_out, ff, ff, 1, self.down_each, ff, d * ff, sel_e, down_out, d, d, pairs, d, ff, st)
+        # row (t, k) of down_out is pair t * top + k: the combine kernel's (expert, row) address with buffers of 0 rows
+        ops.moe_combine(down_out, sel_e, sel_pos, sel_w, top, ident, h, d, 0, d, y, d, T, st)
+
     def forward(self, step, h, y, h16_ready=False):
         if self._gathered_pays(step.T):
             return self._forward_gathered(step, h, y, h16_ready)
+        if self._indexed_pays(step.T):
+            return self._forward_indexed(step, h, y)
         c, T, d, N = self.cfg, step.T, self.up.K, self.up.N
         z = step.scratch("ff_z", T * N)
         self.up(step, h.data_ptr(), d, z.data_ptr(), N, a16_ready=h16_ready)

@@ -136,6 +136,13 @@ class Ops:
         self._ck(self.lib.sllm_seq_moe_route(logits_ptr, ldl, n_route, experts, top, _p(correction), _p(h), ldh, d, counts_ptr, cap, sel_e, sel_pos, sel_w, ident,
                                              rows16, rows32, T, st))
 
+    def act(self, x_ptr, n, kind, st):
+        self._ck(self.lib.sllm_seq_act(x_ptr, n, kind, st))
+
+    def linear_indexed(self, a_ptr, lda, a_bs, a_div, w, ldw, w_bs, w_index, c_ptr, ldc, c_bs, batch, N, K, st):
+        """``batch`` products of one row each, product b with the matrix ``w_index[b]`` (device array) of ``w``."""
+        self._ck(self.lib.sllm_seq_linear_indexed(a_ptr, lda, a_bs, a_div, _p(w), self.w_dtype, ldw, w_bs, w_index, c_ptr, ldc, c_bs, batch, N, K, self.round_a, st))
+
     def moe_expert_act(self, up_ptr, counts_ptr, experts, cap, ff, act, out16, out32, st):
         self._ck(self.lib.sllm_seq_moe_expert_act(up_ptr, counts_ptr, experts, cap, ff, act, out16, out32, st))
 

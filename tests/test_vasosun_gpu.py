@@ -376,6 +376,39 @@ def test_experts_with_tokens_gathered_per_expert(dtype, monkeypatch):
         assert _rel(gathered, want) < tol and _rel(every, want) < tol, (mlp, _rel(gathered, want), _rel(every, want))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_experts_chosen_on_the_device_for_single_tokens(dtype, monkeypatch):
+    """Steps of one or two tokens stream only the chosen experts' matrices (one launch per projection, the matrix of every (token, choice)
+    pair picked on the device): the same numbers as the restatement and as the form that computes every expert."""
+    import torch
+
+    from simplellminference_b200 import layers
+    from simplellminference_b200.config import BF16, F32, VasosunConfig
+    from simplellminference_b200.seqops import Ops
+    rng, d = np.random.default_rng(15), 72
+    dev, ops = torch.device("cuda"), Ops(BF16 if dtype == "bfloat16" else F32)
+    for mlp, T in ((L.moe(experts=7, identity=2, top=3, ff=40), 2), (L.moe(experts=9, identity=0, top=1, ff=64), 8), (L.moe(experts=5, identity=4, top=4, ff=13), 1)):
+        cfg = L.make_config([L.attention_layer(mlp=mlp)], width=d)
+        w = L.random_weights(cfg, seed=6)
+        wt = {k: torch.tensor(v, device=dev, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32) for k, v in w.items()}
+        ff = layers.ExpertsFeedForward(VasosunConfig.from_dict(cfg).layers[0].mlp, wt, "l0.mlp.", ops, dev)
+
+        def fn(step, h, states):
+            y = step.scratch("sub_out", step.T * d)
+            ff.forward(step, h, y)
+            return [y[:step.T * d].view(step.T, d)]
+        h = L.bf16_round(2 * rng.standard_normal((3 * T, d))).astype(np.float32)
+        stub = _Stub([{"pages": [], "slots": []}], fn, ops, dev)
+        every = _feed(stub, h, [T, T, T])[0]
+        monkeypatch.setattr(layers.ExpertsFeedForward, "index_launch_cost", 0.0)
+        assert ff._indexed_pays(T)
+        indexed = _feed(stub, h, [T, T, T])[0]
+        monkeypatch.undo()
+        want = O.moe_ff(h.astype(np.float64), _w64(w), "l0.mlp.", mlp)
+        tol = F32_TOL if dtype == "float32" else BF16_MIXER
+        assert _rel(indexed, want) < tol and _rel(every, want) < tol, (mlp, _rel(indexed, want), _rel(every, want))
+
+
 def test_pair_embedding_and_logit_cap(tmp_path):
     """The first token takes the pair table's last row, every other the hashed row of (previous token, token) — also across a cut."""
     cfg = L.make_config([L.attention_layer(mlp=None)], vocab=50, width=32, buckets=7, mul_prev=5, mul_cur=3, softcap=2.0)
