@@ -210,14 +210,21 @@ __global__ void seq_moe_expert_act_kernel(const float* __restrict__ up, const in
 __global__ void seq_moe_combine_kernel(const float* __restrict__ down, const int32_t* __restrict__ sel_e, const int32_t* __restrict__ sel_pos,
                                        const float* __restrict__ sel_w, int top, const float* __restrict__ ident, const float* __restrict__ h, int ldh,
                                        int cap, int d, float* __restrict__ y, int ldy) {
+    extern __shared__ float csm[];                           // [top] score (0 = no row), [top] row offset
+    float* s_w = csm;
+    long long* s_row = reinterpret_cast<long long*>(csm + ((top + 1) & ~1));
     const int t = blockIdx.x;
+    for (int k = threadIdx.x; k < top; k += blockDim.x) {
+        const int e = sel_e[(size_t)t * top + k];
+        s_w[k] = e >= 0 ? sel_w[(size_t)t * top + k] : 0.0f;
+        s_row[k] = e >= 0 ? ((long long)e * cap + sel_pos[(size_t)t * top + k]) * d : -1;
+    }
+    __syncthreads();
     const float idw = ident[t];
     for (int j = threadIdx.x; j < d; j += blockDim.x) {
         float acc = idw * h[(size_t)t * ldh + j];
-        for (int k = 0; k < top; ++k) {                      // in the order of the choice: a fixed order of the sum
-            const int e = sel_e[(size_t)t * top + k];
-            if (e >= 0) acc = fmaf(sel_w[(size_t)t * top + k], down[((size_t)e * cap + sel_pos[(size_t)t * top + k]) * d + j], acc);
-        }
+        for (int k = 0; k < top; ++k)                        // in the order of the choice: a fixed order of the sum
+            if (s_row[k] >= 0) acc = fmaf(s_w[k], down[s_row[k] + j], acc);
         y[(size_t)t * ldy + j] = acc;
     }
 }
@@ -269,7 +276,10 @@ int sllm_seq_moe_expert_act(const float* up, const int32_t* counts, int32_t expe
 int sllm_seq_moe_combine(const float* down, const int32_t* sel_e, const int32_t* sel_pos, const float* sel_w, int32_t top, const float* ident, const float* h,
                          int32_t ldh, int32_t cap, int32_t d, float* y, int32_t ldy, int32_t T, sllm_stream_t stream) {
     SLLM_REQUIRE(down && sel_e && sel_pos && sel_w && ident && h && y && top >= 1 && T > 0 && d > 0, SLLM_EINVAL, "seq_moe_combine: bad argument");
-    seq_moe_combine_kernel<<<T, 256, 0, as_stream(stream)>>>(down, sel_e, sel_pos, sel_w, top, ident, h, ldh, cap, d, y, ldy);
+    SLLM_REQUIRE(top <= 2048, SLLM_ENOTSUP, "seq_moe_combine: top %d beyond 2048", top);
+    const int threads = T >= 64 ? 256 : std::min(1024, std::max(128, (d + 31) / 32 * 32));
+    const size_t smem = (size_t)((top + 1) & ~1) * sizeof(float) + (size_t)top * sizeof(long long);
+    seq_moe_combine_kernel<<<T, threads, smem, as_stream(stream)>>>(down, sel_e, sel_pos, sel_w, top, ident, h, ldh, cap, d, y, ldy);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
