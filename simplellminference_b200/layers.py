@@ -2,7 +2,9 @@
 that a model description can combine them: fused input projections, softmax attention with (scaled, partial) rotary positions, rotated
 values and a head gate over a paged cache; softmax attention with unit-rms heads, capped scores, distance slopes and a window that keeps
 the first positions; latent attention (one cached row per token, absorbed form) with a sink and a head gate; a Griffin-style recurrent block (short causal convolution + real-gated linear recurrent unit);
-gated linear attention with a decay per key channel; a PolyNorm feed-forward; a clamped gated feed-forward. A mechanism says which per-sequence state it needs
+gated linear attention with a decay per key channel; a PolyNorm feed-forward; a clamped gated feed-forward; softmax attention with a charge on the
+logarithm of the distance and a query temperature; the gated delta rule behind short convolutions; a gated (silu) feed-forward and a mixture of
+experts with identity experts. A mechanism says which per-sequence state it needs
 (``state_spec``); the engine's state manager owns that memory and hands it to ``forward`` — no mechanism keeps a cache of its own.
 
 Additive to the reference, whose only model is the Llama forward of source/model/model.cpp:40-140."""

@@ -2,7 +2,8 @@
 
 ``SequenceEngine`` owns, for every layer run of a model, what that run's mixer declares in ``state_spec``: page pools for softmax
 attention (pages handed out by the same bookkeeping as the batched Llama decoder, ``batch.KvPages``) and slot-indexed fp32 state for the
-recurrent mixers. One ``run`` is one step: any mix of portions of prompts and single decoded tokens, each request at its own position.
+recurrent mixers; a layer may also borrow state another layer owns (``"borrow"`` in its ``state_spec``: attention over an earlier
+layer's cache), and the engine keeps each request's last token for models whose embedding looks at the previous one. One ``run`` is one step: any mix of portions of prompts and single decoded tokens, each request at its own position.
 Logits at a position do not depend on how the tokens were cut into steps, on the neighbours in the batch, or on which pages and slot a
 request got, beyond the rounding of differently ordered sums.
 
