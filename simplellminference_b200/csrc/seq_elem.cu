@@ -280,6 +280,16 @@ __global__ void seq_rmsnorm_rows_kernel(const float* x, int ldx, const float* __
     for (int j = lane; j < n; j += 32) y[(size_t)t * ldy + j] = (xr[j] * inv) * (w ? w[j] : 1.0f);
 }
 
+// the same with one CTA per row, for steps of few rows (one warp would walk a long row alone)
+__global__ void seq_rmsnorm_row_cta_kernel(const float* x, int ldx, const float* __restrict__ w, float eps, float* y, int ldy, int n) {   // y may be x
+    __shared__ float red[33];
+    const float* xr = x + (size_t)blockIdx.x * ldx;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) ss = fmaf(xr[j], xr[j], ss);
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)n + eps);
+    for (int j = threadIdx.x; j < n; j += blockDim.x) y[(size_t)blockIdx.x * ldy + j] = (xr[j] * inv) * (w ? w[j] : 1.0f);
+}
+
 // out = act(gate) * up; act 0 = silu
 __global__ void seq_gated_act_kernel(const float* __restrict__ gate, int ldg, const float* __restrict__ up, int ldu, int act, float* __restrict__ out,
                                      int ldo, uint16_t* __restrict__ out16, int T, int n) {
@@ -435,7 +445,8 @@ int sllm_seq_embed_pair(const int32_t* ids, const int32_t* prev_ids, const void*
 
 int sllm_seq_rmsnorm_rows(const float* x, int32_t ldx, const float* w, float eps, float* y, int32_t ldy, int32_t T, int32_t n, sllm_stream_t stream) {
     SLLM_REQUIRE(x && y && T > 0 && n > 0 && ldx >= n && ldy >= n, SLLM_EINVAL, "seq_rmsnorm_rows: bad argument");
-    seq_rmsnorm_rows_kernel<<<(T + 3) / 4, 128, 0, as_stream(stream)>>>(x, ldx, w, eps, y, ldy, T, n);
+    if (T < 64 && n > 128) seq_rmsnorm_row_cta_kernel<<<T, std::min(1024, (n + 31) / 32 * 32), 0, as_stream(stream)>>>(x, ldx, w, eps, y, ldy, n);
+    else seq_rmsnorm_rows_kernel<<<(T + 3) / 4, 128, 0, as_stream(stream)>>>(x, ldx, w, eps, y, ldy, T, n);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

@@ -136,7 +136,8 @@ def _mixer_stub(layer_cfgs, w, width, dtype="float32", eps=1e-5):
 ALONE = [L.attention_layer(), L.attention_layer(heads=3, kv_heads=3, dim=20, vdim=36, size=9, every=0), L.attention_layer(heads=8, kv_heads=1, dim=8, vdim=8, size=64, scale=1.0, every=2),
          L.attention_layer(size=None), L.latent_layer(), L.latent_layer(heads=1, dim=24, rot_dim=4, vdim=70, kv_rank=72, q_rank=5),
          L.latent_layer(heads=5, dim=4, rot_dim=16, rot_dims=6, vdim=12, kv_rank=20, scaling=None), L.delta_layer(), L.delta_layer(heads=1, kv_heads=1, dim=100, vdim=5, conv=1),
-         L.delta_layer(heads=6, kv_heads=2, dim=8, vdim=33, conv=6), L.delta_layer(heads=2, kv_heads=1, dim=300, vdim=5, conv=2)]
+         L.delta_layer(heads=6, kv_heads=2, dim=8, vdim=33, conv=6), L.delta_layer(heads=2, kv_heads=1, dim=300, vdim=5, conv=2),
+         L.latent_layer(heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=16, q_rank=200)]
 
 
 def _oracle_mixer(layer_cfg, w, h, pre="l0.mix.", kv=None):
