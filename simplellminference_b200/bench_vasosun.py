@@ -30,7 +30,7 @@ def vasosun_config(width: int, repeats: int, vocab: int = 32000) -> dict:
     ff = ((8 * width // 3) + 255) // 256 * 256
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": EXPERTS, "identity": IDENTITY, "top": TOP}}
-    rot = {"dims": 64, "base": 1e6, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    rot = {"dims": 64, "base": 500000.0, "scaling": {"factor": 4.0, "original": 8192, "fast": 16.0, "slow": 2.0}}
     layers = []
     for r in range(repeats):
         att = {"type": "attention", "mlp": dense,
