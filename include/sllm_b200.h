@@ -467,6 +467,8 @@ typedef struct {
     const float* slopes;     /* [heads] or NULL: score <- score - slopes[h] * (i - j), after the cap */
     int32_t values_in_keys;  /* != 0: a value row is the first dv columns of the key row (one pool; v_pool is not read) */
     const float* logdist;    /* [2][heads] or NULL: score <- score - r1[h] * ln(1 + r2[h] * (i - j)) with r1 = row 0, r2 = row 1 */
+    int32_t cross_values;    /* != 0: every query head's weights are applied to the values of EVERY key/value head (the keys it reads stay
+                              * those of its own): ws holds kv_heads * heads records per token, record (value head * heads + query head) */
 } sllm_seq_attn_opts;
 /* Causal softmax attention of every token over positions 0..pos of its own sequence: score = (q . k) * scale, query head h reads
  * key/value head h / (heads / kv_heads). Keys are visited in tiles of 32, cut into nsplit interleaved shares; the partial results
@@ -516,14 +518,19 @@ int sllm_seq_softcap(float* x, int64_t n, float cap, sllm_stream_t stream);
  * the step's rows and, before a portion, into ring [slots][taps-1][d] (position p at row p % (taps-1)); h16 (or NULL) = h as dense
  * bf16 rows; (3) the normed rows of every portion's last taps-1 tokens go to stash [T][d]; a later call with flush_ring (the ring this
  * call read) moves them there. rms(v) = sqrt(mean(v^2) + eps). scales (or NULL): T floats of scratch; with it, steps of 64 tokens and
- * more run as two launches (sum and per-row scale, then the convolution element-wise) so that no row is normed more than once. */
+ * more run as two launches (sum and per-row scale, then the convolution element-wise) so that no row is normed more than once.
+ * post_norm 0: the sum takes y as it is, x_out = x_in + y (a pre-norm layer). pre_w (or NULL) [d]: a weight per channel on the normed
+ * row, stored as its distance from pre_w_offset: n[c] = pre_g * (pre_w_offset + pre_w[c]) * x[c] / rms(x). */
 int sllm_seq_seam(const sllm_seq_batch* b, const float* x_in, float* x_out, const float* y, float post_g, int32_t has_pre, float pre_g,
                   float eps, const float* conv_w, int32_t taps, const float* ring, float* h, void* h16, float* stash, float* flush_ring,
-                  int32_t flush_taps, int32_t d, float* scales, sllm_stream_t stream);
-/* out[t][c] = act(sum_j w[c][j] * x[t - taps + 1 + j][c]) (act 0 = none, 1 = silu), zeros before a sequence's start; inputs before a
- * portion come from ring [slots][taps-1][channels] (position p at row p % (taps-1)), which is NOT updated here */
-int sllm_seq_conv_ring(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, const float* w, const float* ring,
-                       int32_t act, float* out, int32_t ldo, sllm_stream_t stream);
+                  int32_t flush_taps, int32_t d, float* scales, int32_t post_norm, const float* pre_w, float pre_w_offset, sllm_stream_t stream);
+/* out[t][c] = act(cb[c] + sum_j w[c][j] * x[t - taps + 1 + j][c]) (cb NULL = no bias; act 0 = none, 1 = silu), zeros before a sequence's
+ * start; inputs before a portion come from ring [slots][taps-1][channels] (position p at row p % (taps-1)), which is NOT updated here
+ * (sllm_seq_delta_rule, sllm_seq_ssd_scan, sllm_seq_selective_scan and sllm_seq_ring_store do that, after the convolution has run) */
+int sllm_seq_conv_ring(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, const float* w, const float* cb,
+                       const float* ring, int32_t act, float* out, int32_t ldo, sllm_stream_t stream);
+/* ring[slot][p % (taps-1)][:] <- x[t][0 .. channels) for the last taps-1 tokens of every portion (p = the token's position) */
+int sllm_seq_ring_store(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, float* ring, sllm_stream_t stream);
 /* Gated delta rule per head h over each sequence, state [slots][heads][dk][dv] fp32: S <- g S; u = beta (v - S^T k); S <- S + k u^T;
  * o = S^T q, with q, k (of key head h / (heads / kv_heads)) divided by sqrt(sum(x^2) + unit_eps), q times qscale,
  * beta = sigmoid(beta_logit), g = exp(-exp(A_log[h]) * softplus(step_logit + dt_bias[h])). ring (or NULL): the last taps-1 rows of
@@ -532,6 +539,39 @@ int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, co
                         const float* beta_logit, int32_t ldb, const float* step_logit, int32_t lda, const float* A_log, const float* dt_bias,
                         int32_t heads, int32_t kv_heads, int32_t dk, int32_t dv, float unit_eps, float qscale, float* state, float* o,
                         int32_t ldo, const float* conv_x, int32_t ldx, int32_t channels, int32_t taps, float* ring, sllm_stream_t stream);
+/* State-space duality (Mamba-2) per head h over each sequence, state [slots][heads][n_state][dv] fp32: dt = softplus(step_logit + dt_bias[h]),
+ * S <- exp(-exp(A_log[h]) dt) S + dt B x^T, y = S^T C + skip[h] x (skip NULL = no such term); x [T][heads * dv], B and C
+ * [T][groups * n_state], head h reads group h / (heads / groups). The kernel of sllm_seq_delta_rule without its correction term; ring as there. */
+int sllm_seq_ssd_scan(const sllm_seq_batch* b, const float* x, int32_t ldx, const float* B, int32_t ldb, const float* C, int32_t ldc,
+                      const float* step_logit, int32_t lda, const float* A_log, const float* dt_bias, const float* skip, int32_t heads, int32_t groups,
+                      int32_t n_state, int32_t dv, float* state, float* y, int32_t ldy, const float* conv_x, int32_t ld_conv, int32_t channels,
+                      int32_t taps, float* ring, sllm_stream_t stream);
+/* Selective scan (Mamba) per channel c over each sequence, state [slots][inner][n_state] fp32: dt = softplus(step_logit[c]),
+ * S[c][n] <- exp(-dt exp(A_log[c][n])) S[c][n] + dt x[c] B[n], y[c] = sum_n S[c][n] C[n] + D[c] x[c], out = y * silu(z); B and C [T][n_state]
+ * are shared by the channels. out fp32 [T][ldo] and / or out16 dense bf16 [T][inner]. ring (or NULL): the last taps-1 rows of conv_x
+ * [T][inner] of every portion are stored there for the convolution of the next step. n_state <= 128. */
+int sllm_seq_selective_scan(const sllm_seq_batch* b, const float* x, int32_t ldx, const float* step_logit, int32_t lddt, const float* B, int32_t ldb,
+                            const float* C, int32_t ldc, const float* z, int32_t ldz, const float* A_log, const float* D, int32_t inner,
+                            int32_t n_state, float* state, float* out, int32_t ldo, void* out16, const float* conv_x, int32_t ld_conv, int32_t taps,
+                            float* ring, sllm_stream_t stream);
+/* Query and key heads RMS-normed over their dk dimensions with a weight [dk] shared by the heads (q_norm_w / k_norm_w, NULL = that kind
+ * is not normed), then their first 2*n_freq dimensions turned by pos * freq[i] (layout and angles as in sllm_seq_rotary_kv); q in place,
+ * k to its pool; v [T][kv_heads * dv] goes to its pool as it is (it may be k itself: values that are the keys before norm and rotation). */
+int sllm_seq_normed_rotary_kv(const sllm_seq_batch* b, float* q, int32_t ldq, int32_t heads, int32_t dk, const float* k, int32_t ldk,
+                              int32_t kv_heads, const float* v, int32_t ldv, int32_t dv, const float* q_norm_w, const float* k_norm_w, float eps,
+                              const double* freq, int32_t n_freq, int32_t layout, void* k_pool, void* v_pool, int32_t kv_dtype,
+                              sllm_stream_t stream);
+/* Heads mixed after the attention: in [T][kv_heads * heads * dv] as sllm_seq_attention_finish leaves it for cross_values (record = value
+ * head * heads + query head); out[t][h] = sum_g mix[h][g] * in[t][(h / (heads / kv_heads)) * heads + g]: head h's mixed weights on the
+ * values of its own key/value head. out fp32 [T][ldo] and / or out16 dense bf16 [T][heads * dv]. */
+int sllm_seq_head_mix(const float* in, int32_t ldi, const float* mix, int32_t heads, int32_t kv_heads, int32_t dv, float* out, int32_t ldo,
+                      void* out16, int32_t T, sllm_stream_t stream);
+/* Bits of the `act` argument of the mixture-of-experts calls beside the activation (bits 0-1): scores = sigmoid of each router output by
+ * itself instead of the softmax over all; gated experts, whose `up` columns are [gate ff | up ff] and which compute act(gate) * up; the
+ * score multiplies what the expert reads instead of what it returns. */
+#define SLLM_MOE_GATED 4
+#define SLLM_MOE_SCALE_INPUT 8
+#define SLLM_MOE_SIGMOID 16
 /* Routing and activation of a mixture of experts, per token: s = softmax(logits[0..n_route)); the `top` largest s + correction are
  * chosen (correction NULL = none; the lower index wins a tie); out / out16 [T][experts * ff] = act(up) * s for chosen experts with
  * weights (the first `experts` router outputs), zeros for the others; y [T][d] = (sum of s over chosen router outputs >= experts) * h:
@@ -548,7 +588,7 @@ int sllm_seq_moe_act(const float* logits, int32_t ldl, int32_t n_route, int32_t 
  * up [experts][cap][ff]. sllm_seq_moe_combine: y[t] = ident[t] * h[t] + sum_k sel_w * down[sel_e][sel_pos] (down [experts][cap][d]). */
 int sllm_seq_moe_route(const float* logits, int32_t ldl, int32_t n_route, int32_t experts, int32_t top, const float* correction, const float* h,
                        int32_t ldh, int32_t d, int32_t* counts, int32_t cap, int32_t* sel_e, int32_t* sel_pos, float* sel_w, float* ident,
-                       void* rows16, float* rows32, int32_t T, sllm_stream_t stream);
+                       void* rows16, float* rows32, int32_t T, int32_t act, sllm_stream_t stream);
 int sllm_seq_moe_expert_act(const float* up, const int32_t* counts, int32_t experts, int32_t cap, int32_t ff, int32_t act, void* out16,
                             float* out32, sllm_stream_t stream);
 int sllm_seq_moe_combine(const float* down, const int32_t* sel_e, const int32_t* sel_pos, const float* sel_w, int32_t top, const float* ident,
@@ -589,9 +629,11 @@ int sllm_seq_rglru_scan(const sllm_seq_batch* b, const float* u, int32_t ldu, co
 int sllm_seq_gla_scan(const sllm_seq_batch* b, const float* q, int32_t ldq, const float* k, int32_t ldk, const float* v, int32_t ldv,
                       const float* z, int32_t ldz, int32_t heads, int32_t dk, int32_t dv, float qscale, float tau, float* state, float* o,
                       int32_t ldo, void* scratch, sllm_stream_t stream);
-/* out[t][h*dv + j] = o[t][h*dv + j] / sqrt(mean_j(o^2) + eps) * w[j] * silu(g[t][h*dv + j]) */
+/* out[t][h*dv + j] = o[t][h*dv + j] / sqrt(mean_j(o^2) + eps) * w[j] * silu(g[t][h*dv + j]). mode bit 0: the gate comes first,
+ * u = o * silu(g), out = u / sqrt(mean_j(u^2) + eps) * w; bit 1: w has heads * dv entries (one per channel of the row) instead of dv.
+ * out fp32 and / or out16 dense bf16 [T][heads * dv]. */
 int sllm_seq_headnorm_gate(const float* o, int32_t ldo, const float* g, int32_t ldg, const float* w, int32_t heads, int32_t dv, float eps,
-                           float* out, int32_t ldout, int32_t T, sllm_stream_t stream);
+                           float* out, int32_t ldout, void* out16, int32_t T, int32_t mode, sllm_stream_t stream);
 
 #ifdef __cplusplus
 }

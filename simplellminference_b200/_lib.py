@@ -126,7 +126,7 @@ class SeqBatch(C.Structure):
 class SeqAttnOpts(C.Structure):
     """sllm_seq_attn_opts: window / kept first positions / score cap / distance slopes / values inside the key rows / a charge on the
     logarithm of the distance."""
-    _fields_ = [("window", _I), ("keep_first", _I), ("softcap", _F), ("slopes", _P), ("values_in_keys", _I), ("logdist", _P)]
+    _fields_ = [("window", _I), ("keep_first", _I), ("softcap", _F), ("slopes", _P), ("values_in_keys", _I), ("logdist", _P), ("cross_values", _I)]
 
 
 _B = C.POINTER(SeqBatch)
@@ -136,7 +136,7 @@ SIGNATURES.update({
     "sllm_seq_hyper_write": (C.c_int, [_P, _I, _I, _I, _P, _P, _P, _P]),
     "sllm_seq_hyper_write_read": (C.c_int, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _F, _P, _P]),
     "sllm_seq_linear": (C.c_int, [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _L, _L, _L, _L, _P, _I, _P, _P]),
-    "sllm_seq_moe_route": (C.c_int, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P]),
+    "sllm_seq_moe_route": (C.c_int, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _P]),
     "sllm_seq_moe_expert_act": (C.c_int, [_P, _P, _I, _I, _I, _I, _P, _P, _P]),
     "sllm_seq_moe_combine": (C.c_int, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _I, _I, _P]),
     "sllm_seq_zero": (C.c_int, [_P, _L, _P]),
@@ -154,8 +154,13 @@ SIGNATURES.update({
     "sllm_seq_rmsnorm_rows": (C.c_int, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
     "sllm_seq_gated_act": (C.c_int, [_P, _I, _P, _I, _I, _P, _I, _P, _I, _I, _P]),
     "sllm_seq_softcap": (C.c_int, [_P, _L, _F, _P]),
-    "sllm_seq_seam": (C.c_int, [_B, _P, _P, _P, _F, _I, _F, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _P, _P]),
-    "sllm_seq_conv_ring": (C.c_int, [_B, _P, _I, _I, _I, _P, _P, _I, _P, _I, _P]),
+    "sllm_seq_seam": (C.c_int, [_B, _P, _P, _P, _F, _I, _F, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _F, _P]),
+    "sllm_seq_conv_ring": (C.c_int, [_B, _P, _I, _I, _I, _P, _P, _P, _I, _P, _I, _P]),
+    "sllm_seq_ring_store": (C.c_int, [_B, _P, _I, _I, _I, _P, _P]),
+    "sllm_seq_ssd_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P]),
+    "sllm_seq_selective_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _I, _P, _P, _I, _I, _P, _P]),
+    "sllm_seq_normed_rotary_kv": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _F, _P, _I, _I, _P, _P, _I, _P]),
+    "sllm_seq_head_mix": (C.c_int, [_P, _I, _P, _I, _I, _I, _P, _I, _P, _I, _P]),
     "sllm_seq_delta_rule": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _F, _F, _P, _P, _I, _P, _I, _I, _I, _P, _P]),
     "sllm_seq_moe_act": (C.c_int, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P, _I, _P]),
     "sllm_seq_layernorm": (C.c_int, [_P, _I, _P, _P, _F, _P, _I, _P, _I, _I, _P]),
@@ -164,11 +169,11 @@ SIGNATURES.update({
     "sllm_seq_conv": (C.c_int, [_B, _P, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
     "sllm_seq_rglru_scan": (C.c_int, [_B, _P, _I, _P, _P, _I, _P, _I, _P, _F, _I, _P, _P, _I, _I, _P, _P, _I, _P, _P]),
     "sllm_seq_gla_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P, _P, _I, _P, _P]),
-    "sllm_seq_headnorm_gate": (C.c_int, [_P, _I, _P, _I, _P, _I, _I, _F, _P, _I, _I, _P]),
+    "sllm_seq_headnorm_gate": (C.c_int, [_P, _I, _P, _I, _P, _I, _I, _F, _P, _I, _P, _I, _I, _P]),
 })
 
 # The ragged-token-batch part of the library can be built and loaded on its own (`make -C csrc seq` -> libsllm_b200_seq.so: the
-# sllm_seq_* kernels, the tensor-core GEMM, the page bookkeeping, the sampler): a model made of those blocks then needs twelve
+# sllm_seq_* kernels, the tensor-core GEMM, the page bookkeeping, the sampler): a model made of those blocks then needs thirteen
 # translation units compiled, not all of them. The full library contains the same objects and is preferred when it exists.
 SEQ_LIB_PATH = os.path.join(HERE, "lib", "libsllm_b200_seq.so")
 SEQ_SYMBOL_PREFIXES = ("sllm_seq_", "sllm_kvpages_", "sllm_sample_", "sllm_last_error", "sllm_abi_version", "sllm_tune", "sllm_device_info",

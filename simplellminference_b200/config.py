@@ -376,7 +376,115 @@ class VasosunConfig:
                              int(pair.get("mul_cur") or 0), float(c.get("logit_softcap") or 0.0), tuple(layers))
 
 
-CONFIG_READERS = {"Munazen": MunazenConfig.from_dict, "Sopetar": SopetarConfig.from_dict, "Vasosun": VasosunConfig.from_dict}
+
+@dataclass(frozen=True)
+class StateSpaceDualityConfig:
+    """Mamba-2: ``heads`` heads of ``vdim`` channels, a state of ``state`` numbers per channel, B and C shared by the heads of each of the
+    ``groups`` groups, a causal convolution of ``conv`` taps over x, B and C, the output normed in ``norm_groups`` equal parts."""
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    norm_groups: int
+    conv: int
+
+
+@dataclass(frozen=True)
+class SelectiveScanConfig:
+    """Mamba: ``inner`` channels with a state of ``state`` numbers each, step sizes through a projection of rank ``dt_rank``, a causal
+    convolution of ``conv`` taps over x."""
+    inner: int
+    state: int
+    dt_rank: int
+    conv: int
+
+
+@dataclass(frozen=True)
+class TalkingHeadsAttentionConfig:
+    """Softmax attention with a convolution and a per-head norm on q and k, values that are the keys before the norm, partial rotary
+    positions (``rot`` None = none), a sliding window that keeps the first positions, and heads mixed after the softmax."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: RotaryConfig | None
+    mask: WindowMask
+    conv: int
+
+
+@dataclass(frozen=True)
+class BiasedFeedForwardConfig:
+    ff: int
+
+
+@dataclass(frozen=True)
+class KodezenLayerConfig:
+    type: str            # "mamba2" | "mamba1" | "attention"
+    mixer: object        # StateSpaceDualityConfig | SelectiveScanConfig | TalkingHeadsAttentionConfig
+    mlp: object = None   # BiasedFeedForwardConfig | ExpertsConfig | None
+
+
+@dataclass(frozen=True)
+class KodezenConfig:
+    """The Kodezen design: pre-norm layers (RMS norms whose weights are stored around zero) whose mixer reads its normed input through a
+    short causal convolution; mixers are Mamba-2 (state-space duality), Mamba (selective scan) and softmax attention with convolved,
+    normed and partly rotated queries and keys, keys as values and heads mixed after the softmax; feed-forwards are dense (biases, exact
+    gelu) or a mixture of gated experts whose sigmoid scores multiply the experts' inputs. Every size and constant that may differ
+    comes from config.json."""
+    architecture: str
+    vocab: int
+    width: int
+    norm_eps: float
+    conv_taps: int
+    embedding_scale: float
+    layers: tuple
+
+    @staticmethod
+    def from_dict(c: dict) -> "KodezenConfig":
+        layers = []
+        for i, l in enumerate(c["layers"]):
+            m, mlp = l["mixer"], l.get("mlp")
+            kind = l["type"]
+            if kind == "mamba2":
+                heads, groups = int(m["heads"]), int(m.get("groups") or 1)
+                if heads % groups:
+                    raise ValueError(f"layer {i}: {heads} heads do not divide over {groups} groups")
+                mixer = StateSpaceDualityConfig(heads, int(m["vdim"]), int(m["state"]), groups, int(m.get("norm_groups") or 1), int(m.get("conv") or 1))
+            elif kind == "mamba1":
+                mixer = SelectiveScanConfig(int(m["inner"]), int(m["state"]), int(m["dt_rank"]), int(m.get("conv") or 1))
+            elif kind == "attention":
+                heads = int(m["heads"])
+                kv_heads = int(m.get("kv_heads") or heads)
+                if heads % kv_heads:
+                    raise ValueError(f"layer {i}: {heads} query heads do not divide over {kv_heads} key/value heads")
+                rot = m.get("rot")
+                rot = RotaryConfig(int(rot["dims"]), float(rot["base"]), None) if rot and int(rot.get("dims") or 0) > 0 else None
+                dim = int(m["dim"])
+                if rot is not None and (rot.dims > dim or rot.dims % 2):
+                    raise ValueError(f"layer {i}: {rot.dims} rotary dimensions do not fit heads of {dim}")
+                mixer = TalkingHeadsAttentionConfig(heads, kv_heads, dim, int(m.get("vdim") or dim), float(m["scale"]), rot, WindowMask.from_dict(m.get("mask")),
+                                                    int(m.get("conv") or 1))
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            ff = None
+            if mlp is not None:
+                if mlp.get("kind", "dense") == "dense":
+                    ff = BiasedFeedForwardConfig(int(mlp["ff"]))
+                elif mlp["kind"] == "moe":
+                    r = mlp["router"]
+                    ff = ExpertsConfig(int(r["experts"]), 0, int(r["top"]), int(mlp["expert"]["ff"]))
+                    if not 1 <= ff.top <= ff.experts:
+                        raise ValueError(f"layer {i}: {ff.top} of {ff.experts} experts")
+                else:
+                    raise ValueError(f"layer {i}: feed-forward kind {mlp['kind']!r} is not part of this design")
+            layers.append(KodezenLayerConfig(kind, mixer, ff))
+        return KodezenConfig(c["architecture"], int(c["vocab"]), int(c["width"]), float((c.get("norm") or {}).get("eps", 1e-6)),
+                             int((c.get("canon") or {}).get("taps") or 1), float((c.get("embedding") or {}).get("scale", 1.0)), tuple(layers))
+
+
+CONFIG_READERS = {"Munazen": MunazenConfig.from_dict, "Sopetar": SopetarConfig.from_dict, "Vasosun": VasosunConfig.from_dict,
+                  "Kodezen": KodezenConfig.from_dict}
 
 
 def read_model_config(model_dir: str):

@@ -33,6 +33,9 @@ struct AttnArgs {
     const float* slopes;      // [heads] or NULL: score <- score - slopes[h] * (i - j)
     int v_in_k;               // values = the first dv columns of the key rows (v_pool unused)
     const float* logdist;     // [2][heads] or NULL: score <- score - r1[h] * ln(1 + r2[h] * (i - j)), r1 = row 0, r2 = row 1
+    // Every query head's weights on every key/value head's values: `heads` then counts kv_heads * q_heads results, result u = (value
+    // head u / q_heads, query head u % q_heads); the query head reads the KEYS of its own key/value head as always. Otherwise q_heads = heads.
+    int q_heads, cross;
 };
 
 // The key tiles a CTA whose queries lie at positions first .. last has to visit: the tiles of the kept first positions, then the tiles
@@ -71,21 +74,23 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
     const sllm_seq_batch& b = p.b;
     const int qt = blockIdx.x, split = blockIdx.z;
     const int seg = b.qt_seg[qt], off = b.qt_off[qt];
-    const int group = p.heads / p.kv_heads;
+    const int group = p.q_heads / p.kv_heads;
     const int t0 = b.seg_start[seg] + off, pos0 = b.seg_pos0[seg] + off, slot = b.seg_slot[seg];
     // row r of the CTA's query tile is (token t0 + r, head blockIdx.y), or with by_head (token t0, head blockIdx.y * group + r)
     const int nq = p.by_head ? group : min(kBQ, b.seg_len[seg] - off);
-    const int g = p.by_head ? blockIdx.y : blockIdx.y / group;
+    const int g = p.by_head ? blockIdx.y : (blockIdx.y % p.q_heads) / group;   // key head
+    const int gv = p.cross ? blockIdx.y / p.q_heads : g;                         // value head
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const KV* kp = reinterpret_cast<const KV*>(p.k_pool);
     const KV* vp = reinterpret_cast<const KV*>(p.v_pool);
     auto row_token = [&](int r) { return p.by_head ? t0 : t0 + r; };
-    auto row_head = [&](int r) { return p.by_head ? (int)blockIdx.y * group + r : (int)blockIdx.y; };
+    auto row_head = [&](int r) { return p.by_head ? (int)blockIdx.y * group + r : (int)blockIdx.y; };                   // the result's number
+    auto row_qhead = [&](int r) { return p.by_head ? (int)blockIdx.y * group + r : (int)blockIdx.y % p.q_heads; };      // the query head behind it
     auto row_pos = [&](int r) { return p.by_head ? pos0 : pos0 + r; };
 
     for (int i = threadIdx.x; i < kBQ * dkp; i += blockDim.x) {
         const int r = i / dkp, c = i % dkp;
-        sq[i] = (r < nq && c < dk) ? p.q[(size_t)row_token(r) * p.ldq + (size_t)row_head(r) * dk + c] : 0.0f;
+        sq[i] = (r < nq && c < dk) ? p.q[(size_t)row_token(r) * p.ldq + (size_t)row_qhead(r) * dk + c] : 0.0f;
     }
     float m[kQW], l[kQW], acc[kQW][kMaxDvChunks];
 #pragma unroll
@@ -97,13 +102,13 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
     }
     float slope[kQW];
 #pragma unroll
-    for (int i = 0; i < kQW; ++i) slope[i] = (p.slopes && warp * kQW + i < nq) ? p.slopes[row_head(warp * kQW + i)] : 0.0f;
+    for (int i = 0; i < kQW; ++i) slope[i] = (p.slopes && warp * kQW + i < nq) ? p.slopes[row_qhead(warp * kQW + i)] : 0.0f;
     float r1[kQW], r2[kQW];
 #pragma unroll
     for (int i = 0; i < kQW; ++i) {
         const bool has = p.logdist && warp * kQW + i < nq;
-        r1[i] = has ? p.logdist[row_head(warp * kQW + i)] : 0.0f;
-        r2[i] = has ? p.logdist[p.heads + row_head(warp * kQW + i)] : 0.0f;
+        r1[i] = has ? p.logdist[row_qhead(warp * kQW + i)] : 0.0f;
+        r2[i] = has ? p.logdist[p.q_heads + row_qhead(warp * kQW + i)] : 0.0f;
     }
     const int last_pos = row_pos(nq - 1);
     const TileList tiles(row_pos(0), last_pos, p.window, p.keep_first, kBK);
@@ -112,7 +117,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
         const int page = b.block_table[(size_t)slot * b.max_pages + j0 / b.page_len], in_page = j0 % b.page_len;
         const int valid = min(kBK, last_pos + 1 - j0);   // keys of this tile that exist
         __syncthreads();
-        const size_t krow = seq_pool_row(page, p.kv_heads, g, b.page_len, in_page, dk), vrow = seq_pool_row(page, p.kv_heads, g, b.page_len, in_page, dv);
+        const size_t krow = seq_pool_row(page, p.kv_heads, g, b.page_len, in_page, dk), vrow = seq_pool_row(page, p.kv_heads, gv, b.page_len, in_page, dv);
         constexpr int E = 16 / sizeof(KV);   // elements per 16-byte load
         if (dk % E == 0 && (dv % E == 0 || p.v_in_k)) {
             // the tile's rows are consecutive in the pool: 16-byte loads, rows beyond `valid` zero-filled (dk is a multiple of 4 here, so the
@@ -249,7 +254,9 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     // two warps (16 queries each) per head; a CTA of four warps serves two query heads of the same kv head from one staged tile
     const int hpc = blockDim.x >> 6, h = blockIdx.y * hpc + (warp >> 1), wq = warp & 1;
-    const int gkv = h / (p.heads / p.kv_heads);
+    const int hq = h % p.q_heads;                      // the query head behind result h
+    const int gkv = hq / (p.q_heads / p.kv_heads);
+    const int gvv = p.cross ? h / p.q_heads : gkv;     // value head
     const int dks = kExact ? kMmaDkSteps : dk / 16, dvt = kExact ? kMmaDvTiles : dv / 8;
     const uint16_t* kp = reinterpret_cast<const uint16_t*>(p.k_pool);
     const uint16_t* vp = reinterpret_cast<const uint16_t*>(p.v_pool);
@@ -257,8 +264,8 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
     const bool ok0 = r0 < nq, ok1 = r1 < nq;
     const int last_pos = pos0 + nq - 1;
     const TileList tiles(pos0, last_pos, p.window, p.keep_first, kBK);
-    const float slope = p.slopes ? p.slopes[h] : 0.0f;
-    const float ld1 = p.logdist ? p.logdist[h] : 0.0f, ld2 = p.logdist ? p.logdist[p.heads + h] : 0.0f;
+    const float slope = p.slopes ? p.slopes[hq] : 0.0f;
+    const float ld1 = p.logdist ? p.logdist[hq] : 0.0f, ld2 = p.logdist ? p.logdist[p.q_heads + hq] : 0.0f;
 
     // tile kt of the sequence -> stage `st` of shared memory, asynchronously (rows beyond the last position are zero-filled)
     auto issue = [&](int kt, int st) {
@@ -266,7 +273,7 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
         const int page = b.block_table[(size_t)slot * b.max_pages + j0 / b.page_len], in_page = j0 % b.page_len;
         const int valid = min(kBK, last_pos + 1 - j0);
         const uint16_t* ksrc = kp + seq_pool_row(page, p.kv_heads, gkv, b.page_len, in_page, dk);
-        const uint16_t* vsrc = vp + seq_pool_row(page, p.kv_heads, gkv, b.page_len, in_page, dv);
+        const uint16_t* vsrc = vp + seq_pool_row(page, p.kv_heads, gvv, b.page_len, in_page, dv);
         uint16_t* sK = smh + st * stage_elems;
         uint16_t* sV = sK + kBK * ldk;
         for (int i = threadIdx.x; i < kBK * (dk / 8); i += blockDim.x) {
@@ -285,8 +292,8 @@ __global__ void __launch_bounds__(128) seq_attention_mma_kernel(AttnArgs p) {
 #pragma unroll
     for (int ks = 0; ks < kMmaDkSteps; ++ks) {
         if (ks < dks) {
-            const float* q0 = p.q + (size_t)(t0 + r0) * p.ldq + (size_t)h * dk + ks * 16 + 2 * c;
-            const float* q1 = p.q + (size_t)(t0 + r1) * p.ldq + (size_t)h * dk + ks * 16 + 2 * c;
+            const float* q0 = p.q + (size_t)(t0 + r0) * p.ldq + (size_t)hq * dk + ks * 16 + 2 * c;
+            const float* q1 = p.q + (size_t)(t0 + r1) * p.ldq + (size_t)hq * dk + ks * 16 + 2 * c;
             qf[ks][0] = ok0 ? pack_bf16(q0[0], q0[1]) : 0u;
             qf[ks][1] = ok1 ? pack_bf16(q1[0], q1[1]) : 0u;
             qf[ks][2] = ok0 ? pack_bf16(q0[8], q0[9]) : 0u;
@@ -577,7 +584,12 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
     const int dkp = ((dk + 3) & ~3) + 4;
     const size_t smem = ((size_t)(kBQ + kBK) * dkp + (v_in_k ? 0 : (size_t)kBK * dv)) * sizeof(float);
     SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes(), SLLM_ENOTSUP, "seq_attention: heads of %d + %d floats need %zu bytes of shared memory", dk, dv, smem);
-    AttnArgs p{*b, q, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws, 0, INT_MAX, 0, 0.0f, nullptr, 0, nullptr};
+    AttnArgs p{*b, q, ldq, heads, kv_heads, dk, dv, scale, k_pool, v_pool, nsplit, ws, 0, INT_MAX, 0, 0.0f, nullptr, 0, nullptr, heads, 0};
+    if (opts && opts->cross_values) {
+        SLLM_REQUIRE(!v_in_k, SLLM_EINVAL, "seq_attention: values of every head need a value pool");
+        p.cross = 1;
+        p.heads = heads * kv_heads;        // results; ws holds that many records per token
+    }
     if (opts) {
         p.window = opts->window > 0 ? opts->window : INT_MAX;
         p.keep_first = opts->window > 0 ? opts->keep_first : 0;
@@ -586,12 +598,12 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
         p.v_in_k = v_in_k;
         p.logdist = opts->logdist;
     }
-    dim3 grid(b->n_qtiles, heads, nsplit);
+    dim3 grid(b->n_qtiles, p.heads, nsplit);
     // steps that hold a portion of a prompt, bf16 pools, head widths the fragments take: the tensor-core body
     if (kv_dtype == SLLM_BF16 && b->T > b->nseg && dk % 16 == 0 && dk <= 192 && dv % 8 == 0 && dv <= 128 && g_tune_seq_attn_mma) {
         const size_t smem_mma = 2 * (size_t)kBK * (dk + 8 + (v_in_k ? 0 : dv + 8)) * sizeof(uint16_t);
         const int hpc = (heads / kv_heads) % 2 == 0 ? 2 : 1;   // query heads per CTA
-        grid.y = heads / hpc;
+        grid.y = p.heads / hpc;
         const dim3 block(64 * hpc);
         cudaStream_t st = as_stream(stream);
         if (dk == 128 && dv == 128) seq_attention_mma_kernel<8, 16, true><<<grid, block, smem_mma, st>>>(p);
@@ -603,7 +615,7 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
         SLLM_LAUNCH_CHECK();
         return SLLM_OK;
     }
-    if (b->T == b->nseg && heads / kv_heads <= kBQ) {   // single tokens only: the query heads of a kv head share one CTA and its tiles
+    if (b->T == b->nseg && heads / kv_heads <= kBQ && !p.cross) {   // single tokens only: the query heads of a kv head share one CTA and its tiles
         p.by_head = 1;
         grid.y = kv_heads;
     }

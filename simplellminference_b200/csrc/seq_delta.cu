@@ -6,6 +6,10 @@
 // up to 32 columns of one head, a thread owns a piece (32 key channels) of one column in registers; the pieces of a column sit in
 // adjacent lanes and meet by shuffles. More CTAs per head means more of the machine per sequence: the token loop itself is serial.
 //
+// The same kernel, instantiated without the correction term, runs the state-space-duality recurrence (Mamba-2): per head
+//     S <- g S + dt B x^T;  y = S^T C + D x,   dt = softplus(a + dt_bias), g = exp(-exp(A_log) dt)
+// with B in the place of k, C in the place of q (neither made a unit vector), x in the place of v, and the heads of a group sharing B and C.
+//
 // The convolution keeps its last taps-1 inputs per sequence in a ring (position p at row p % (taps-1)); the recurrence kernel, which
 // runs after the convolution has read the ring, stores the portion's last inputs there.
 #include <cstdlib>
@@ -14,13 +18,13 @@
 
 namespace sllm {
 
-// thread = (token, channel): out = act(sum_j w[c][j] * x[t - taps + 1 + j][c]); act 0 = none, 1 = silu
+// thread = (token, channel): out = act(cb[c] + sum_j w[c][j] * x[t - taps + 1 + j][c]); act 0 = none, 1 = silu
 __global__ void seq_conv_ring_kernel(sllm_seq_batch b, const float* __restrict__ x, int ldx, int channels, int taps, const float* __restrict__ w,
-                                     const float* __restrict__ ring, int act, float* __restrict__ out, int ldo) {
+                                     const float* __restrict__ cb, const float* __restrict__ ring, int act, float* __restrict__ out, int ldo) {
     const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= channels) return;
     const int slot = b.tok_slot[t], pos = b.tok_pos[t];
-    float acc = w[(size_t)c * taps + taps - 1] * x[(size_t)t * ldx + c];
+    float acc = fmaf(w[(size_t)c * taps + taps - 1], x[(size_t)t * ldx + c], cb ? cb[c] : 0.0f);
     for (int back = 1; back < taps; ++back) {
         if (pos - back < 0) break;
         const float xv = (t - back >= 0 && b.tok_slot[t - back] == slot) ? x[(size_t)(t - back) * ldx + c]
@@ -42,6 +46,7 @@ struct DeltaArgs {
     float* o; int ldo;                                  // [T][heads * dv]
     const float* conv_x; int ldx, channels, taps; float* ring;   // inputs of the convolution, stored to the ring for the next step (NULL = not)
     int chunk, PP, CB, vec;
+    const float* skip;                                  // state-space form: [heads] weight of the input added to the output (NULL = none)
 };
 
 // key channels of a thread: 16 for key heads of up to 512 channels (measured best of 8 / 16 / 32 at 128-wide heads), 32 for wider ones.
@@ -58,7 +63,8 @@ __device__ __forceinline__ void delta_cp4(void* dst, const void* src, bool take)
 }
 
 // CTA = (segment, head, block of CB value columns); thread = (value column j, piece `part` of the key channels), part = tid % PP
-template <int kDeltaKP, int kMaxThreads>
+// kSsd: the state-space form (no correction by the old state, no unit vectors, the step size multiplies the input)
+template <int kDeltaKP, int kMaxThreads, bool kSsd>
 __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
     constexpr int kDeltaRS = kDeltaKP + 4;
     extern __shared__ __align__(16) float dsm[];
@@ -119,6 +125,7 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
         S[x] = (live && kr < dk) ? st[(size_t)kr * dv + j] : 0.0f;
     }
     const float rate = expf(p.A_log[h]), bias = p.dt_bias[h];
+    const float skip = (kSsd && p.skip) ? p.skip[h] : 0.0f;
     issue(0, 0);
     int stage = 0;
     for (int c0 = 0; c0 < len; c0 += C, stage ^= 1) {
@@ -131,8 +138,9 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
         const float* s_v = s_q + C * RS;               // [C][CB]
         const float* s_l = s_v + C * CBp;              // [C][2]
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            s_beta[i] = seq_sigmoid(s_l[2 * i]);
-            s_g[i] = expf(-rate * seq_softplus(s_l[2 * i + 1] + bias));
+            const float dt = seq_softplus(s_l[2 * i + 1] + bias);
+            s_beta[i] = kSsd ? dt : seq_sigmoid(s_l[2 * i]);
+            s_g[i] = expf(-rate * dt);
         }
         for (int tok = warp; tok < n; tok += nwarps) {                             // unit vectors: a warp per token
             float sk = 0.0f, sq = 0.0f, skq = 0.0f;
@@ -142,8 +150,12 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
                 sq = fmaf(s_q[at], s_q[at], sq);
                 skq = fmaf(s_k[at], s_q[at], skq);
             }
-            const float ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps), iq = p.qscale / sqrtf(warp_sum(sq) + p.unit_eps);
             skq = warp_sum(skq);
+            if (kSsd) {                                                             // B and C enter as they are
+                if (lane == 0) s_kq[tok] = skq;
+                continue;
+            }
+            const float ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps), iq = p.qscale / sqrtf(warp_sum(sq) + p.unit_eps);
             if (lane == 0) s_kq[tok] = (skq * ik) * iq;
             for (int kr = lane; kr < PP * kDeltaKP; kr += 32) {
                 const int at = tok * RS + (kr / kDeltaKP) * kDeltaRS + kr % kDeltaKP;
@@ -168,17 +180,18 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
                 kr[x] = kv.x; kr[x + 1] = kv.y; kr[x + 2] = kv.z; kr[x + 3] = kv.w;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    d4[e] = fmaf(S[x + e], kr[x + e], d4[e]);
+                    if (!kSsd) d4[e] = fmaf(S[x + e], kr[x + e], d4[e]);
                     e4[e] = fmaf(S[x + e], qr[e], e4[e]);
                 }
             }
             float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]), dq = (e4[0] + e4[1]) + (e4[2] + e4[3]);
             for (int o = PP >> 1; o > 0; o >>= 1) {
-                dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                if (!kSsd) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 dq += __shfl_xor_sync(0xffffffffu, dq, o);
             }
-            const float u = beta * ((live ? s_v[i * CB + jl] : 0.0f) - g * dot);
-            if (live && part == 0) s_o[i * CB + jl] = fmaf(u, kq, g * dq);
+            const float vin = live ? s_v[i * CB + jl] : 0.0f;
+            const float u = kSsd ? beta * vin : beta * (vin - g * dot);
+            if (live && part == 0) s_o[i * CB + jl] = fmaf(u, kq, g * dq) + skip * vin;
 #pragma unroll
             for (int x = 0; x < kDeltaKP; ++x) S[x] = fmaf(kr[x], u, g * S[x]);
         }
@@ -210,23 +223,26 @@ using namespace sllm;
 
 extern "C" {
 
-int sllm_seq_conv_ring(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, const float* w, const float* ring, int32_t act,
-                       float* out, int32_t ldo, sllm_stream_t stream) {
+int sllm_seq_conv_ring(const sllm_seq_batch* b, const float* x, int32_t ldx, int32_t channels, int32_t taps, const float* w, const float* cb,
+                       const float* ring, int32_t act, float* out, int32_t ldo, sllm_stream_t stream) {
     SLLM_REQUIRE(b && b->T > 0 && b->tok_slot && b->tok_pos, SLLM_EINVAL, "seq_conv_ring: incomplete batch description");
     SLLM_REQUIRE(x && w && out && channels > 0 && taps >= 1 && (taps == 1 || ring) && (act == 0 || act == 1), SLLM_EINVAL, "seq_conv_ring: bad argument");
     SLLM_REQUIRE(b->T <= 65535, SLLM_ENOTSUP, "seq_conv_ring: at most 65535 tokens per step");
-    seq_conv_ring_kernel<<<dim3((channels + 127) / 128, b->T), 128, 0, as_stream(stream)>>>(*b, x, ldx, channels, taps, w, ring, act, out, ldo);
+    seq_conv_ring_kernel<<<dim3((channels + 127) / 128, b->T), 128, 0, as_stream(stream)>>>(*b, x, ldx, channels, taps, w, cb, ring, act, out, ldo);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
 }
 
-int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, const float* k, int32_t ldk, const float* v, int32_t ldv, const float* beta_logit,
-                        int32_t ldb, const float* step_logit, int32_t lda, const float* A_log, const float* dt_bias, int32_t heads, int32_t kv_heads,
-                        int32_t dk, int32_t dv, float unit_eps, float qscale, float* state, float* o, int32_t ldo, const float* conv_x, int32_t ldx,
-                        int32_t channels, int32_t taps, float* ring, sllm_stream_t stream) {
+}  // extern "C"
+
+// both recurrences: `ssd` = the state-space form (skip [heads] or NULL)
+static int delta_run(bool ssd, const float* skip, const sllm_seq_batch* b, const float* q, int32_t ldq, const float* k, int32_t ldk, const float* v, int32_t ldv,
+                     const float* beta_logit, int32_t ldb, const float* step_logit, int32_t lda, const float* A_log, const float* dt_bias, int32_t heads,
+                     int32_t kv_heads, int32_t dk, int32_t dv, float unit_eps, float qscale, float* state, float* o, int32_t ldo, const float* conv_x,
+                     int32_t ldx, int32_t channels, int32_t taps, float* ring, sllm_stream_t stream) {
     SLLM_REQUIRE(b && b->T > 0 && b->nseg > 0 && b->seg_start && b->seg_len && b->seg_slot && b->seg_pos0, SLLM_EINVAL, "seq_delta_rule: incomplete batch description");
-    SLLM_REQUIRE(q && k && v && beta_logit && step_logit && A_log && dt_bias && state && o, SLLM_EINVAL, "seq_delta_rule: bad argument");
+    SLLM_REQUIRE(q && k && v && beta_logit && step_logit && A_log && dt_bias && state && o, SLLM_EINVAL, "seq_delta_rule / seq_ssd_scan: bad argument");
     SLLM_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0, SLLM_EINVAL, "seq_delta_rule: %d heads over %d key heads", heads, kv_heads);
     SLLM_REQUIRE(!ring || (conv_x && channels > 0 && taps >= 1), SLLM_EINVAL, "seq_delta_rule: the ring needs the convolution's inputs");
     static const int tune_kp = getenv("SLLM_DELTA_KP") ? atoi(getenv("SLLM_DELTA_KP")) : 0;      // measurement aids: 8 / 16 / 32 channels per thread,
@@ -255,20 +271,44 @@ int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, co
     SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes() - 2048, SLLM_ENOTSUP, "seq_delta_rule: one token of a %d x %d head needs %zu bytes of shared memory", dk, dv, smem);
     const int vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0;
     DeltaArgs p{*b, q, k, v, ldq, ldk, ldv, beta_logit, step_logit, ldb, lda, A_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale, state, o, ldo,
-                conv_x, ldx, channels, taps, ring, chunk, PP, CB, vec};
-#define SLLM_DELTA_LAUNCH(KPV, MAXT)                                                                                                              \
-    do {                                                                                                                                          \
-        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_delta_kernel<KPV, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        seq_delta_kernel<KPV, MAXT><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);                                       \
+                conv_x, ldx, channels, taps, ring, chunk, PP, CB, vec, skip};
+#define SLLM_DELTA_LAUNCH_AS(KPV, MAXT, SSD)                                                                                                             \
+    do {                                                                                                                                                 \
+        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_delta_kernel<KPV, MAXT, SSD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        seq_delta_kernel<KPV, MAXT, SSD><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);                                         \
+    } while (0)
+#define SLLM_DELTA_LAUNCH(KPV, MAXT)                 \
+    do {                                             \
+        if (ssd) SLLM_DELTA_LAUNCH_AS(KPV, MAXT, true); \
+        else SLLM_DELTA_LAUNCH_AS(KPV, MAXT, false);    \
     } while (0)
     if (KP == 8) SLLM_DELTA_LAUNCH(8, 1024);
     else if (KP == 16) SLLM_DELTA_LAUNCH(16, 512);
     else if (threads <= 256) SLLM_DELTA_LAUNCH(32, 256);
     else SLLM_DELTA_LAUNCH(32, 1024);
 #undef SLLM_DELTA_LAUNCH
+#undef SLLM_DELTA_LAUNCH_AS
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;
+}
+
+extern "C" {
+
+int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, const float* k, int32_t ldk, const float* v, int32_t ldv, const float* beta_logit,
+                        int32_t ldb, const float* step_logit, int32_t lda, const float* A_log, const float* dt_bias, int32_t heads, int32_t kv_heads,
+                        int32_t dk, int32_t dv, float unit_eps, float qscale, float* state, float* o, int32_t ldo, const float* conv_x, int32_t ldx,
+                        int32_t channels, int32_t taps, float* ring, sllm_stream_t stream) {
+    return delta_run(false, nullptr, b, q, ldq, k, ldk, v, ldv, beta_logit, ldb, step_logit, lda, A_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale, state,
+                     o, ldo, conv_x, ldx, channels, taps, ring, stream);
+}
+
+int sllm_seq_ssd_scan(const sllm_seq_batch* b, const float* x, int32_t ldx, const float* B, int32_t ldb, const float* C, int32_t ldc, const float* step_logit,
+                      int32_t lda, const float* A_log, const float* dt_bias, const float* skip, int32_t heads, int32_t groups, int32_t n_state, int32_t dv,
+                      float* state, float* y, int32_t ldy, const float* conv_x, int32_t ld_conv, int32_t channels, int32_t taps, float* ring,
+                      sllm_stream_t stream) {
+    return delta_run(true, skip, b, C, ldc, B, ldb, x, ldx, step_logit, lda, step_logit, lda, A_log, dt_bias, heads, groups, n_state, dv, 0.0f, 1.0f, state, y, ldy,
+                     conv_x, ld_conv, channels, taps, ring, stream);
 }
 
 }  // extern "C"

@@ -138,18 +138,28 @@ __global__ void seq_gather_rows_kernel(const float* __restrict__ x, int ldx, con
 
 // one warp per (token, head)
 __global__ void seq_headnorm_gate_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ g, int ldg, const float* __restrict__ w,
-                                         int heads, int dv, float eps, float* __restrict__ out, int ldout, int T) {
+                                         int heads, int dv, float eps, float* __restrict__ out, int ldout, uint16_t* __restrict__ out16, int T, int mode) {
     const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (item >= T * heads) return;
     const int t = item / heads, h = item % heads;
     const float* orow = o + (size_t)t * ldo + (size_t)h * dv;
+    const float* grow = g + (size_t)t * ldg + (size_t)h * dv;
+    const float* wrow = (mode & 2) ? w + (size_t)h * dv : w;      // a weight per channel of the whole row, or one set shared by the parts
+    const bool gate_first = mode & 1;                             // the gate multiplies before the root mean square is taken
     float ss = 0.0f;
-    for (int j = lane; j < dv; j += 32) ss = fmaf(orow[j], orow[j], ss);
+    for (int j = lane; j < dv; j += 32) {
+        const float gv = grow[j];
+        const float v = gate_first ? orow[j] * (gv / (1.0f + expf(-gv))) : orow[j];
+        ss = fmaf(v, v, ss);
+    }
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
     for (int j = lane; j < dv; j += 32) {
-        const float gv = g[(size_t)t * ldg + (size_t)h * dv + j];
-        out[(size_t)t * ldout + (size_t)h * dv + j] = ((orow[j] * inv) * w[j]) * (gv / (1.0f + expf(-gv)));
+        const float gv = grow[j];
+        const float sg = gv / (1.0f + expf(-gv));
+        const float v = gate_first ? ((orow[j] * sg) * inv) * wrow[j] : ((orow[j] * inv) * wrow[j]) * sg;
+        if (out) out[(size_t)t * ldout + (size_t)h * dv + j] = v;
+        if (out16) out16[(size_t)t * heads * dv + (size_t)h * dv + j] = f32_to_bf16_bits(v);
     }
 }
 
@@ -384,10 +394,10 @@ int sllm_seq_gather_rows(const float* x, int32_t ldx, const int32_t* rows, int32
 }
 
 int sllm_seq_headnorm_gate(const float* o, int32_t ldo, const float* g, int32_t ldg, const float* w, int32_t heads, int32_t dv, float eps, float* out,
-                           int32_t ldout, int32_t T, sllm_stream_t stream) {
-    SLLM_REQUIRE(o && g && w && out && heads > 0 && dv > 0 && T > 0, SLLM_EINVAL, "seq_headnorm_gate: bad argument");
+                           int32_t ldout, void* out16, int32_t T, int32_t mode, sllm_stream_t stream) {
+    SLLM_REQUIRE(o && g && w && (out || out16) && heads > 0 && dv > 0 && T > 0 && mode >= 0 && mode <= 3, SLLM_EINVAL, "seq_headnorm_gate: bad argument");
     const int items = T * heads;
-    seq_headnorm_gate_kernel<<<(items + 3) / 4, 128, 0, as_stream(stream)>>>(o, ldo, g, ldg, w, heads, dv, eps, out, ldout, T);
+    seq_headnorm_gate_kernel<<<(items + 3) / 4, 128, 0, as_stream(stream)>>>(o, ldo, g, ldg, w, heads, dv, eps, out, ldout, (uint16_t*)out16, T, mode);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

@@ -4,11 +4,18 @@
 // CHOICE only, picks the `top` largest, and writes act(up) * score for the chosen real experts (zeros for the others) as the operand of
 // ONE down product over the concatenated experts. The last `identity` router outputs are experts without weights whose output is the
 // input itself: their scores are summed and the kernel leaves (sum * input) in the output rows, to which the down product is added.
+// Variants, chosen by bits of the `mode` argument beside the activation: scores that are the sigmoid of each router output by itself
+// (SLLM_MOE_SIGMOID) instead of a softmax over all; gated experts (SLLM_MOE_GATED: an expert's `up` columns are [gate ff | up ff] and
+// it computes act(gate) * up); a score that multiplies what the expert reads instead of what it returns (SLLM_MOE_SCALE_INPUT: the
+// products are linear, so gate and up are multiplied after the product in the dense form, the gathered rows before it).
 #include "seq_common.cuh"
 
 namespace sllm {
 
+constexpr int kMoeGated = 4, kMoeScaleInput = 8, kMoeSigmoid = 16;   // SLLM_MOE_* of the header
+
 __device__ __forceinline__ float moe_act(float z, int kind) {
+    kind &= 3;
     if (kind == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));   // exact gelu
     if (kind == 1) return seq_gelu_tanh(z);
     return z * seq_sigmoid(z);                                                   // silu
@@ -26,17 +33,22 @@ __global__ void seq_moe_act_kernel(const float* __restrict__ logits, int ldl, in
     const int t = blockIdx.x, lane = threadIdx.x & 31;
     const float* z = logits + (size_t)t * ldl;
     if (threadIdx.x < 32) {
-        float mx = -INFINITY;
-        for (int e = lane; e < n_route; e += 32) mx = fmaxf(mx, z[e]);
-        mx = warp_max(mx);
-        float sum = 0.0f;
-        for (int e = lane; e < n_route; e += 32) {
-            const float v = expf(z[e] - mx);
-            s_score[e] = v;
-            sum += v;
+        float inv = 1.0f;
+        if (act & kMoeSigmoid) {
+            for (int e = lane; e < n_route; e += 32) s_score[e] = seq_sigmoid(z[e]);
+        } else {
+            float mx = -INFINITY;
+            for (int e = lane; e < n_route; e += 32) mx = fmaxf(mx, z[e]);
+            mx = warp_max(mx);
+            float sum = 0.0f;
+            for (int e = lane; e < n_route; e += 32) {
+                const float v = expf(z[e] - mx);
+                s_score[e] = v;
+                sum += v;
+            }
+            sum = warp_sum(sum);
+            inv = 1.0f / sum;
         }
-        sum = warp_sum(sum);
-        const float inv = 1.0f / sum;
         for (int e = lane; e < n_route; e += 32) {
             const float s = s_score[e] * inv;
             s_score[e] = s;
@@ -71,9 +83,16 @@ __global__ void seq_moe_act_kernel(const float* __restrict__ logits, int ldl, in
         for (int e = threadIdx.x; e < n_route; e += blockDim.x) route_w[(size_t)t * n_route + e] = s_w[e];
     const float* ur = up + (size_t)t * ldu;
     const size_t orow = (size_t)t * experts * ff;
+    const bool gated = act & kMoeGated, on_input = act & kMoeScaleInput;
     for (int i = threadIdx.x; i < experts * ff; i += blockDim.x) {
-        const float w = s_w[i / ff];
-        const float v = w != 0.0f ? moe_act(ur[i], act) * w : 0.0f;
+        const int e = i / ff;
+        const float w = s_w[e];
+        float v = 0.0f;
+        if (w != 0.0f) {
+            const float pre = on_input ? w : 1.0f, post = on_input ? 1.0f : w;
+            if (gated) v = moe_act(ur[(size_t)e * 2 * ff + i % ff] * pre, act) * (ur[(size_t)e * 2 * ff + ff + i % ff] * pre) * post;
+            else v = moe_act(ur[i] * pre, act) * post;
+        }
         if (out) out[orow + i] = v;
         if (out16) out16[orow + i] = f32_to_bf16_bits(v);
     }
@@ -91,7 +110,7 @@ extern "C" int sllm_seq_moe_act(const float* logits, int32_t ldl, int32_t n_rout
     SLLM_REQUIRE(logits && up && h && y && (out || out16) && T > 0 && ff > 0 && d > 0, SLLM_EINVAL, "seq_moe_act: bad argument");
     SLLM_REQUIRE(experts >= 0 && n_route >= experts && n_route > 0 && top >= 1 && top <= n_route, SLLM_EINVAL, "seq_moe_act: %d of %d router outputs, %d experts with weights",
                  top, n_route, experts);
-    SLLM_REQUIRE(act >= 0 && act <= 2, SLLM_EINVAL, "seq_moe_act: activation 0 (gelu), 1 (tanh gelu) or 2 (silu)");
+    SLLM_REQUIRE(act >= 0 && (act & 3) <= 2 && act < 32, SLLM_EINVAL, "seq_moe_act: activation 0 (gelu), 1 (tanh gelu) or 2 (silu), plus SLLM_MOE_* bits");
     SLLM_REQUIRE(n_route <= 4096, SLLM_ENOTSUP, "seq_moe_act: %d router outputs beyond 4096", n_route);
     const int work = std::max(experts * ff, d);
     const int threads = T >= 64 ? 256 : std::min(1024, std::max(128, (work + 31) / 32 * 32));
@@ -109,7 +128,7 @@ extern "C" int sllm_seq_moe_act(const float* logits, int32_t ldl, int32_t n_rout
 // the device: sllm_seq_linear's rows_dev); the combine kernel adds each token's rows, times their scores, to (identity scores) * input.
 namespace sllm {
 
-__global__ void seq_moe_route_kernel(const float* __restrict__ logits, int ldl, int n_route, int experts, int top, const float* __restrict__ correction,
+__global__ void seq_moe_route_kernel(int act, const float* __restrict__ logits, int ldl, int n_route, int experts, int top, const float* __restrict__ correction,
                                      const float* __restrict__ h, int ldh, int d, int32_t* __restrict__ counts, int cap, int32_t* __restrict__ sel_e,
                                      int32_t* __restrict__ sel_pos, float* __restrict__ sel_w, float* __restrict__ ident_out, uint16_t* __restrict__ rows16,
                                      float* __restrict__ rows32) {
@@ -118,20 +137,26 @@ __global__ void seq_moe_route_kernel(const float* __restrict__ logits, int ldl, 
     float* s_choice = msm + n_route;
     int* s_e = reinterpret_cast<int*>(msm + 2 * n_route);   // [top] expert of the k-th choice, -1 = an expert without weights
     int* s_pos = s_e + top;                                 // [top] its row in that expert's buffer
+    float* s_in = reinterpret_cast<float*>(s_pos + top);    // [top] what the gathered row is multiplied by
     const int t = blockIdx.x, lane = threadIdx.x & 31;
     const float* z = logits + (size_t)t * ldl;
     if (threadIdx.x < 32) {
-        float mx = -INFINITY;
-        for (int e = lane; e < n_route; e += 32) mx = fmaxf(mx, z[e]);
-        mx = warp_max(mx);
-        float sum = 0.0f;
-        for (int e = lane; e < n_route; e += 32) {
-            const float v = expf(z[e] - mx);
-            s_score[e] = v;
-            sum += v;
+        float inv = 1.0f;
+        if (act & kMoeSigmoid) {
+            for (int e = lane; e < n_route; e += 32) s_score[e] = seq_sigmoid(z[e]);
+        } else {
+            float mx = -INFINITY;
+            for (int e = lane; e < n_route; e += 32) mx = fmaxf(mx, z[e]);
+            mx = warp_max(mx);
+            float sum = 0.0f;
+            for (int e = lane; e < n_route; e += 32) {
+                const float v = expf(z[e] - mx);
+                s_score[e] = v;
+                sum += v;
+            }
+            sum = warp_sum(sum);
+            inv = 1.0f / sum;
         }
-        sum = warp_sum(sum);
-        const float inv = 1.0f / sum;
         for (int e = lane; e < n_route; e += 32) {
             const float s = s_score[e] * inv;
             s_score[e] = s;
@@ -169,7 +194,9 @@ __global__ void seq_moe_route_kernel(const float* __restrict__ logits, int ldl, 
                 s_pos[k] = pos;
                 sel_e[(size_t)t * top + k] = e_out;
                 sel_pos[(size_t)t * top + k] = pos;
-                sel_w[(size_t)t * top + k] = e_out >= 0 ? w : 0.0f;
+                // a score that multiplies the expert's input is applied to the gathered row; the combine kernel then adds the rows as they are
+                sel_w[(size_t)t * top + k] = e_out >= 0 ? ((act & kMoeScaleInput) ? 1.0f : w) : 0.0f;
+                s_in[k] = (act & kMoeScaleInput) ? w : 1.0f;
             }
             __syncwarp();
         }
@@ -182,9 +209,10 @@ __global__ void seq_moe_route_kernel(const float* __restrict__ logits, int ldl, 
         const int e = s_e[k];
         if (e < 0) continue;
         const size_t row = ((size_t)e * cap + s_pos[k]) * d;
+        const float mul = s_in[k];
         for (int j = threadIdx.x; j < d; j += blockDim.x) {
-            if (rows16) rows16[row + j] = f32_to_bf16_bits(hr[j]);
-            if (rows32) rows32[row + j] = hr[j];
+            if (rows16) rows16[row + j] = f32_to_bf16_bits(hr[j] * mul);
+            if (rows32) rows32[row + j] = hr[j] * mul;
         }
     }
 }
@@ -200,8 +228,9 @@ __global__ void seq_moe_expert_act_kernel(const float* __restrict__ up, const in
     const int e = blockIdx.y, r = blockIdx.x;
     if (r >= counts[e]) return;
     const size_t row = ((size_t)e * cap + r) * ff;
+    const bool gated = act & kMoeGated;                  // rows of `up` then hold [gate ff | up ff]
     for (int j = threadIdx.x; j < ff; j += blockDim.x) {
-        const float v = moe_act(up[row + j], act);
+        const float v = gated ? moe_act(up[2 * row + j], act) * up[2 * row + ff + j] : moe_act(up[row + j], act);
         if (out16) out16[row + j] = f32_to_bf16_bits(v);
         if (out32) out32[row + j] = v;
     }
@@ -249,14 +278,14 @@ int sllm_seq_zero(void* p, int64_t n_bytes, sllm_stream_t stream) {
 
 int sllm_seq_moe_route(const float* logits, int32_t ldl, int32_t n_route, int32_t experts, int32_t top, const float* correction, const float* h, int32_t ldh,
                        int32_t d, int32_t* counts, int32_t cap, int32_t* sel_e, int32_t* sel_pos, float* sel_w, float* ident, void* rows16, float* rows32,
-                       int32_t T, sllm_stream_t stream) {
+                       int32_t T, int32_t mode, sllm_stream_t stream) {
     SLLM_REQUIRE(logits && h && sel_e && sel_pos && sel_w && ident && T > 0 && d > 0, SLLM_EINVAL, "seq_moe_route: bad argument");
     SLLM_REQUIRE((counts != nullptr) == (rows16 || rows32), SLLM_EINVAL, "seq_moe_route: counters and row buffers come together");
     SLLM_REQUIRE(experts >= 0 && n_route >= experts && n_route > 0 && top >= 1 && top <= n_route && cap >= T, SLLM_EINVAL,
                  "seq_moe_route: %d of %d router outputs, %d experts with weights, buffers of %d rows for %d tokens", top, n_route, experts, cap, T);
     SLLM_REQUIRE(n_route <= 4096 && top <= 1024, SLLM_ENOTSUP, "seq_moe_route: %d router outputs / top %d beyond what one CTA routes", n_route, top);
-    const size_t smem = (2 * (size_t)n_route + 2 * (size_t)top) * sizeof(float);
-    seq_moe_route_kernel<<<T, 256, smem, as_stream(stream)>>>(logits, ldl, n_route, experts, top, correction, h, ldh, d, counts, cap, sel_e, sel_pos, sel_w, ident,
+    const size_t smem = (2 * (size_t)n_route + 3 * (size_t)top) * sizeof(float);
+    seq_moe_route_kernel<<<T, 256, smem, as_stream(stream)>>>(mode, logits, ldl, n_route, experts, top, correction, h, ldh, d, counts, cap, sel_e, sel_pos, sel_w, ident,
                                                                (uint16_t*)rows16, rows32);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
@@ -265,7 +294,7 @@ int sllm_seq_moe_route(const float* logits, int32_t ldl, int32_t n_route, int32_
 
 int sllm_seq_moe_expert_act(const float* up, const int32_t* counts, int32_t experts, int32_t cap, int32_t ff, int32_t act, void* out16, float* out32,
                             sllm_stream_t stream) {
-    SLLM_REQUIRE(up && counts && (out16 || out32) && experts > 0 && cap > 0 && cap <= 65535 * 32 && ff > 0 && act >= 0 && act <= 2, SLLM_EINVAL, "seq_moe_expert_act: bad argument");
+    SLLM_REQUIRE(up && counts && (out16 || out32) && experts > 0 && cap > 0 && cap <= 65535 * 32 && ff > 0 && act >= 0 && (act & 3) <= 2, SLLM_EINVAL, "seq_moe_expert_act: bad argument");
     SLLM_REQUIRE(experts <= 65535, SLLM_ENOTSUP, "seq_moe_expert_act: %d experts", experts);
     seq_moe_expert_act_kernel<<<dim3(cap, experts), 256, 0, as_stream(stream)>>>(up, counts, cap, ff, act, (uint16_t*)out16, out32);
     ++g_launches;

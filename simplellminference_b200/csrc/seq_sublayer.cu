@@ -1,6 +1,8 @@
 // csrc/seq_sublayer.cu — the seam between two sublayers of a model whose sublayers are wrapped in scalar RMS norms and read their input
 // through a short causal convolution: x <- x + g_post * y / rms(y) (the residual sum, fp32), then h = n + conv(n) with
 // n = g_pre * x / rms(x) and conv a per-channel causal convolution over time, as ONE kernel. A norm here has one number as its weight.
+// The same seam serves pre-norm layers: the sum may take y as it is (no norm on the sublayer's output), and the norm in front of the
+// next sublayer may carry a weight per channel stored as its distance from a constant, n = g_pre * (offset + w[c]) * x / rms(x).
 //
 // The convolution reaches taps-1 tokens back. Inside a portion those are rows of this step: a CTA (one per token) recomputes the
 // residual sum and the norm of its predecessors from the sublayer's input and output (x is therefore read from one buffer and written to
@@ -23,7 +25,11 @@ struct SeamArgs {
     float* stash;                             // [T][d]: normed rows of tokens that a later launch moves into `ring`
     float* flush_ring; int flush_taps;        // the ring that takes the stash the previous seam left
     int d;
+    int post_norm;                            // 0 = y is added as it is
+    const float* pre_w; float pre_off;        // [d] or NULL: channel c of the normed row is also multiplied by pre_off + pre_w[c]
 };
+
+__device__ __forceinline__ float seam_gain(const SeamArgs& p, int j) { return p.pre_w ? p.pre_off + p.pre_w[j] : 1.0f; }
 
 // is token t among the last `keep` tokens of its portion?
 __device__ __forceinline__ bool seam_is_last(const sllm_seq_batch& b, int t, int slot, int keep) {
@@ -56,8 +62,8 @@ __global__ void seq_seam_kernel(SeamArgs p) {
             continue;
         }
         const size_t r = (size_t)(t - back) * d;
-        float inv_y = 0.0f;
-        if (p.y) {
+        float inv_y = 1.0f;
+        if (p.y && p.post_norm) {
             float ss = 0.0f;
             for (int j = threadIdx.x; j < d; j += blockDim.x) ss = fmaf(p.y[r + j], p.y[r + j], ss);
             inv_y = p.post_g / sqrtf(block_sum(ss, red) / (float)d + p.eps);
@@ -76,7 +82,7 @@ __global__ void seq_seam_kernel(SeamArgs p) {
         const float inv = p.pre_g / sqrtf(block_sum(ss, red) / (float)d + p.eps);
         if (!p.conv_w) {
             for (int j = threadIdx.x; j < d; j += blockDim.x) {
-                const float v = s_row[j] * inv;
+                const float v = s_row[j] * inv * seam_gain(p, j);
                 p.h[r + j] = v;
                 if (p.h16) p.h16[r + j] = f32_to_bf16_bits(v);
             }
@@ -84,7 +90,7 @@ __global__ void seq_seam_kernel(SeamArgs p) {
         }
         const bool keep = back == 0 && seam_is_last(b, t, slot, p.taps - 1);
         for (int j = threadIdx.x; j < d; j += blockDim.x) {
-            const float n = s_row[j] * inv;
+            const float n = s_row[j] * inv * seam_gain(p, j);
             float acc = fmaf(p.conv_w[(size_t)j * p.taps + p.taps - 1 - back], n, started ? s_acc[j] : 0.0f);
             if (back == 0) {
                 acc += n;
@@ -116,7 +122,7 @@ __global__ void seq_seam_sum_kernel(SeamArgs p, float* __restrict__ scale) {
             seam_sm[j] = v;
             sy = fmaf(v, v, sy);
         }
-        const float inv_y = p.post_g / sqrtf(block_sum(sy, red) / (float)d + p.eps);
+        const float inv_y = p.post_norm ? p.post_g / sqrtf(block_sum(sy, red) / (float)d + p.eps) : 1.0f;
         for (int j = threadIdx.x; j < d; j += blockDim.x) {
             const float v = fmaf(seam_sm[j], inv_y, p.x_in[r + j]);
             p.x_out[r + j] = v;
@@ -136,6 +142,7 @@ constexpr int kSeamMaxTaps = 64;
 __global__ void seq_seam_conv_kernel(SeamArgs p, const float* __restrict__ scale, int vec) {
     __shared__ const float* s_src[kSeamMaxTaps];   // [back] row that lies `back` positions before the token, NULL = before the sequence's start
     __shared__ float s_mul[kSeamMaxTaps];
+    __shared__ bool back_is_step[kSeamMaxTaps];    // the row is one of this step's (not yet normed) rather than a ring row
     const sllm_seq_batch& b = p.b;
     const int t = blockIdx.x, d = p.d, slot = b.tok_slot[t], pos = b.tok_pos[t], taps = p.taps;
     const float* x = p.y ? p.x_out : p.x_in;             // the stream after the sum
@@ -147,16 +154,19 @@ __global__ void seq_seam_conv_kernel(SeamArgs p, const float* __restrict__ scale
         const int back = threadIdx.x;
         const float* src = nullptr;
         float mul = 1.0f;
+        bool in_step = false;
         if (pos - back >= 0) {
             if (back == 0 || (t - back >= 0 && b.tok_slot[t - back] == slot)) {
                 src = x + r - (size_t)back * d;
                 mul = scale[t - back];
+                in_step = true;
             } else {
                 src = p.ring + ((size_t)slot * (taps - 1) + (pos - back) % (taps - 1)) * d;
             }
         }
         s_src[back] = src;
         s_mul[back] = mul;
+        back_is_step[back] = in_step;
     }
     __syncthreads();
     const float own = s_mul[0];
@@ -164,17 +174,20 @@ __global__ void seq_seam_conv_kernel(SeamArgs p, const float* __restrict__ scale
         for (int j = (blockIdx.y * blockDim.x + threadIdx.x) * 4; j < d; j += gridDim.y * blockDim.x * 4) {
             if (flush) *reinterpret_cast<float4*>(fdst + j) = *reinterpret_cast<const float4*>(p.stash + r + j);
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const float gn[4] = {seam_gain(p, j), seam_gain(p, j + 1), seam_gain(p, j + 2), seam_gain(p, j + 3)};
             for (int back = taps - 1; back >= 1; --back) {
                 const float* src = s_src[back];
                 if (!src) continue;
                 const float4 v = *reinterpret_cast<const float4*>(src + j);
                 const float m = s_mul[back];
-                const float n4[4] = {v.x * m, v.y * m, v.z * m, v.w * m};
+                // a ring row is normed and weighted already (its multiplier is 1); a row of this step gets the channel's weight here
+                const bool raw = back_is_step[back];
+                const float n4[4] = {v.x * m * (raw ? gn[0] : 1.0f), v.y * m * (raw ? gn[1] : 1.0f), v.z * m * (raw ? gn[2] : 1.0f), v.w * m * (raw ? gn[3] : 1.0f)};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[e] = fmaf(p.conv_w[(size_t)(j + e) * taps + taps - 1 - back], n4[e], acc[e]);
             }
             const float4 v = *reinterpret_cast<const float4*>(x + r + j);
-            const float n4[4] = {v.x * own, v.y * own, v.z * own, v.w * own};
+            const float n4[4] = {v.x * own * gn[0], v.y * own * gn[1], v.z * own * gn[2], v.w * own * gn[3]};
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[e] = fmaf(p.conv_w[(size_t)(j + e) * taps + taps - 1], n4[e], acc[e]) + n4[e];
             *reinterpret_cast<float4*>(p.h + r + j) = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -190,11 +203,12 @@ __global__ void seq_seam_conv_kernel(SeamArgs p, const float* __restrict__ scale
     for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < d; j += gridDim.y * blockDim.x) {
         if (flush) fdst[j] = p.stash[r + j];
         float acc = 0.0f;
+        const float gn = seam_gain(p, j);
         for (int back = taps - 1; back >= 1; --back) {
             const float* src = s_src[back];
-            if (src) acc = fmaf(p.conv_w[(size_t)j * taps + taps - 1 - back], src[j] * s_mul[back], acc);
+            if (src) acc = fmaf(p.conv_w[(size_t)j * taps + taps - 1 - back], src[j] * s_mul[back] * (back_is_step[back] ? gn : 1.0f), acc);
         }
-        const float n = x[r + j] * own;
+        const float n = x[r + j] * own * gn;
         acc = fmaf(p.conv_w[(size_t)j * taps + taps - 1], n, acc) + n;
         p.h[r + j] = acc;
         if (p.h16) p.h16[r + j] = f32_to_bf16_bits(acc);
@@ -208,7 +222,7 @@ using namespace sllm;
 
 extern "C" int sllm_seq_seam(const sllm_seq_batch* b, const float* x_in, float* x_out, const float* y, float post_g, int32_t has_pre, float pre_g,
                              float eps, const float* conv_w, int32_t taps, const float* ring, float* h, void* h16, float* stash, float* flush_ring,
-                             int32_t flush_taps, int32_t d, float* scales, sllm_stream_t stream) {
+                             int32_t flush_taps, int32_t d, float* scales, int32_t post_norm, const float* pre_w, float pre_w_offset, sllm_stream_t stream) {
     SLLM_REQUIRE(b && b->T > 0 && b->tok_slot && b->tok_pos, SLLM_EINVAL, "seq_seam: incomplete batch description");
     SLLM_REQUIRE(x_in && d > 0 && (!y || (x_out && x_out != x_in)), SLLM_EINVAL, "seq_seam: the residual sum needs a second buffer for x");
     SLLM_REQUIRE(!has_pre || h, SLLM_EINVAL, "seq_seam: no output for the normed rows");
@@ -218,7 +232,7 @@ extern "C" int sllm_seq_seam(const sllm_seq_batch* b, const float* x_in, float* 
     const size_t smem = 2 * (size_t)d * sizeof(float);
     SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes() - 1024, SLLM_ENOTSUP, "seq_seam: rows of %d floats do not fit shared memory", d);
     if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_seam_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    SeamArgs p{*b, x_in, x_out, y, post_g, has_pre, pre_g, eps, conv_w, taps, ring, h, (uint16_t*)h16, stash, flush_ring, flush_taps, d};
+    SeamArgs p{*b, x_in, x_out, y, post_g, has_pre, pre_g, eps, conv_w, taps, ring, h, (uint16_t*)h16, stash, flush_ring, flush_taps, d, post_norm, pre_w, pre_w_offset};
     const int threads = b->T >= 64 ? (d >= 2048 ? 256 : 128) : std::min(1024, std::max(128, (d + 31) / 32 * 32));
     if (scales && has_pre && conv_w && b->T >= 64 && b->T <= 65535) {       // many tokens: two launches, every row normed once
         seq_seam_sum_kernel<<<b->T, threads, smem / 2, as_stream(stream)>>>(p, scales);

@@ -4,7 +4,10 @@ values and a head gate over a paged cache; softmax attention with unit-rms heads
 the first positions; latent attention (one cached row per token, absorbed form) with a sink and a head gate; a Griffin-style recurrent block (short causal convolution + real-gated linear recurrent unit);
 gated linear attention with a decay per key channel; a PolyNorm feed-forward; a clamped gated feed-forward; softmax attention with a charge on the
 logarithm of the distance and a query temperature; the gated delta rule behind short convolutions; a gated (silu) feed-forward and a mixture of
-experts with identity experts. A mechanism says which per-sequence state it needs
+experts with identity experts (softmax or sigmoid scores, plain or gated experts, the score on the expert's output or on its input);
+state-space duality (Mamba-2) and the selective scan (Mamba) behind short convolutions; softmax attention whose queries and keys pass a
+convolution and a per-head norm, whose values are the keys before the norm, and whose weights are mixed over the heads after the softmax;
+a feed-forward with biases and the exact gelu. A mechanism says which per-sequence state it needs
 (``state_spec``); the engine's state manager owns that memory and hands it to ``forward`` — no mechanism keeps a cache of its own.
 
 Additive to the reference, whose only model is the Llama forward of source/model/model.cpp:40-140."""
@@ -349,6 +352,170 @@ class GatedDeltaRule:
         ops.headnorm_gate(o.data_ptr(), self.width, g, ld, self.norm_w, c.heads, c.vdim, self.eps, out, self.width, T, step.st)
 
 
+class StateSpaceDuality:
+    """Mamba-2: ONE input product laid out as [z: inner | x: inner | B: groups * state | C: groups * state | dt: heads], inner = heads * vdim;
+    x, B and C pass a causal convolution (tensor ``conv`` [channels][taps] with bias ``conv.b``) and silu; per head (head h reads group
+    h / (heads / groups)) dt = softplus(dt + dt_bias), S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x; y times silu(z), then RMS-normed
+    in ``norm_groups`` equal parts times the weight ``norm``, then the output projection. State per sequence: S [heads][state][vdim] and
+    the convolution's last taps-1 inputs (a ring indexed by position), fp32."""
+
+    def __init__(self, cfg, w, pre, ops, device, eps):
+        self.cfg, self.ops, self.eps = cfg, ops, eps
+        self.inner = cfg.heads * cfg.vdim
+        self.channels = self.inner + 2 * cfg.groups * cfg.state
+        if int(w[pre + "in"].shape[0]) != self.inner + self.channels + cfg.heads:
+            raise ValueError(f"{pre}in has {int(w[pre + 'in'].shape[0])} rows, the configuration asks for {self.inner + self.channels + cfg.heads}")
+        self.inputs = [(w[pre + "in"], None)]
+        self.conv_w = w[pre + "conv"].float().contiguous()
+        if tuple(self.conv_w.shape) != (self.channels, cfg.conv):
+            raise ValueError(f"{pre}conv is {tuple(self.conv_w.shape)}, the configuration says {(self.channels, cfg.conv)}")
+        self.conv_b = w[pre + "conv.b"].float().contiguous() if pre + "conv.b" in w else None
+        self.a_log = w[pre + "A_log"].float().contiguous()
+        self.dt_bias = w[pre + "dt_bias"].float().contiguous()
+        self.skip = w[pre + "D"].float().contiguous() if pre + "D" in w else None
+        self.norm_w = w[pre + "norm"].float().contiguous()
+        if self.inner % cfg.norm_groups:
+            raise ValueError(f"{self.inner} channels do not divide into {cfg.norm_groups} norm groups")
+        self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
+        self.width = self.inner
+
+    def state_spec(self):
+        c = self.cfg
+        slots = [("S", (c.heads, c.state, c.vdim))]
+        if c.conv > 1:
+            slots.append(("ring", (c.conv - 1, self.channels)))
+        return {"pages": [], "slots": slots}
+
+    def forward(self, step, cols, ld, state, out):
+        c, ops, T, C, inner = self.cfg, self.ops, step.T, self.channels, self.inner
+        z = cols[0]
+        xbc, dt = z + inner * F32B, z + (inner + C) * F32B
+        u = step.scratch("ssd_xbc", T * C)
+        ring = state.get("ring")
+        ops.conv_ring(step.b, xbc, ld, C, c.conv, self.conv_w, ring, 1, u, C, step.st, bias=self.conv_b)
+        gn = c.groups * c.state
+        y = step.scratch("ssd_y", T * inner)
+        ops.ssd_scan(step.b, u.data_ptr(), C, u.data_ptr() + inner * F32B, C, u.data_ptr() + (inner + gn) * F32B, C, dt, ld, self.a_log, self.dt_bias,
+                     self.skip, c.heads, c.groups, c.state, c.vdim, state["S"], y, inner, xbc, ld, C, c.conv, ring, step.st)
+        rows16 = self.out.operand_rows(step)       # the output projection on the tensor cores reads bf16 rows: write those, and only those
+        ops.headnorm_gate(y.data_ptr(), inner, z, ld, self.norm_w, c.norm_groups, inner // c.norm_groups, self.eps, None if rows16 is not None else out, inner,
+                          T, step.st, out16=rows16, gate_first=True, wide_weight=True)
+        return rows16 is not None
+
+
+class SelectiveScan:
+    """Mamba: the input product is [x: inner | z: inner]; x passes a causal convolution (``conv`` with bias ``conv.b``) and silu; W_x x is
+    [dt: dt_rank | B: state | C: state]; dt = softplus(W_dt dt + bias ``dt.b``) per channel; A = -exp(A_log) [inner][state]; per channel c and
+    state n: S[c][n] <- exp(dt_c A[c][n]) S[c][n] + dt_c x_c B_n, y_c = sum_n S[c][n] C_n + D_c x_c; y times silu(z), then the output
+    projection. State per sequence: S [inner][state] and the convolution's last taps-1 inputs (a ring indexed by position), fp32."""
+
+    def __init__(self, cfg, w, pre, ops, device):
+        self.cfg, self.ops = cfg, ops
+        inner = cfg.inner
+        if int(w[pre + "in"].shape[0]) != 2 * inner:
+            raise ValueError(f"{pre}in has {int(w[pre + 'in'].shape[0])} rows, the configuration asks for {2 * inner}")
+        self.inputs = [(w[pre + "in"], None)]
+        self.conv_w = w[pre + "conv"].float().contiguous()
+        if tuple(self.conv_w.shape) != (inner, cfg.conv):
+            raise ValueError(f"{pre}conv is {tuple(self.conv_w.shape)}, the configuration says {(inner, cfg.conv)}")
+        self.conv_b = w[pre + "conv.b"].float().contiguous() if pre + "conv.b" in w else None
+        self.low = FusedLinear([(w[pre + "x"], None)], ops, device, pad_rows=4)
+        if self.low.sizes[0] != cfg.dt_rank + 2 * cfg.state:
+            raise ValueError(f"{pre}x has {self.low.sizes[0]} rows, the configuration asks for {cfg.dt_rank + 2 * cfg.state}")
+        self.step = FusedLinear([(w[pre + "dt"], w.get(pre + "dt.b"))], ops, device)
+        self.a_log = w[pre + "A_log"].float().contiguous()
+        self.skip = w[pre + "D"].float().contiguous()
+        self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
+        self.width = inner
+
+    def state_spec(self):
+        c = self.cfg
+        slots = [("S", (c.inner, c.state))]
+        if c.conv > 1:
+            slots.append(("ring", (c.conv - 1, c.inner)))
+        return {"pages": [], "slots": slots}
+
+    def forward(self, step, cols, ld, state, out):
+        c, ops, T, inner = self.cfg, self.ops, step.T, self.cfg.inner
+        x = cols[0]
+        z = x + inner * F32B
+        u = step.scratch("scan_x", T * inner)
+        ring = state.get("ring")
+        ops.conv_ring(step.b, x, ld, inner, c.conv, self.conv_w, ring, 1, u, inner, step.st, bias=self.conv_b)
+        L = self.low.N
+        low = step.scratch("scan_low", T * L)
+        self.low(step, u.data_ptr(), inner, low.data_ptr(), L)
+        dtl = step.scratch("scan_dt", T * inner)
+        self.step(step, low.data_ptr(), L, dtl.data_ptr(), inner)
+        rows16 = self.out.operand_rows(step)
+        ops.selective_scan(step.b, u.data_ptr(), inner, dtl.data_ptr(), inner, low.data_ptr() + c.dt_rank * F32B, L,
+                           low.data_ptr() + (c.dt_rank + c.state) * F32B, L, z, ld, self.a_log, self.skip, inner, c.state, state["S"],
+                           None if rows16 is not None else out, inner, x, ld, c.conv, ring, step.st, out16=rows16)
+        return rows16 is not None
+
+
+class TalkingHeadsAttention:
+    """Softmax attention over a paged cache with grouped query heads in which: q and k pass a short causal convolution per channel (tensors
+    ``q.conv`` / ``k.conv``, no bias) directly after their projections; the VALUES are the keys as they leave that convolution (there is
+    no value projection); q and k are then RMS-normed per head (weights ``q.norm`` / ``k.norm`` of the head's width) and rotated on their
+    first ``rot.dims`` dimensions (pairs 2i, 2i+1); a sliding window keeps the first positions visible; and after the softmax the heads'
+    weights are mixed, weight_h <- sum_g talk[h][g] weight_g, head h applying its mixed weights to the values of its own key/value head.
+    Computed without ever forming the weights: the attention kernel returns every query head's weights on EVERY key/value head's values
+    (``cross_values``), and the mix is taken over those results. State per sequence: the k and v pools, and the convolution's last
+    taps-1 inputs (a ring indexed by position)."""
+
+    def __init__(self, cfg, w, pre, ops, device, eps):
+        self.cfg, self.ops, self.eps = cfg, ops, eps
+        if cfg.vdim != cfg.dim:
+            raise ValueError(f"values that are the keys need vdim = dim, not {cfg.vdim} and {cfg.dim}")
+        self.inputs = [(w[pre + "q"], w.get(pre + "q.b")), (w[pre + "k"], w.get(pre + "k.b"))]      # adjacent: one convolution runs over both
+        self.nq, self.nk = cfg.heads * cfg.dim, cfg.kv_heads * cfg.dim
+        self.channels = self.nq + self.nk
+        if cfg.conv > 1:
+            self.conv_w = torch.cat([w[pre + "q.conv"].float(), w[pre + "k.conv"].float()], dim=0).contiguous()
+            if tuple(self.conv_w.shape) != (self.channels, cfg.conv):
+                raise ValueError(f"{pre}q.conv / k.conv hold {tuple(self.conv_w.shape)}, the configuration says {(self.channels, cfg.conv)}")
+        else:      # one tap: a weight per channel on the current token, or nothing at all
+            self.conv_w = (torch.cat([w[pre + "q.conv"].float(), w[pre + "k.conv"].float()], dim=0).contiguous() if pre + "q.conv" in w
+                           else torch.ones(self.channels, 1, device=device))
+        self.q_norm = w[pre + "q.norm"].float().contiguous() if pre + "q.norm" in w else None
+        self.k_norm = w[pre + "k.norm"].float().contiguous() if pre + "k.norm" in w else None
+        self.talk = w[pre + "talk"].float().contiguous() if pre + "talk" in w else torch.eye(cfg.heads, device=device)
+        if tuple(self.talk.shape) != (cfg.heads, cfg.heads):
+            raise ValueError(f"{pre}talk is {tuple(self.talk.shape)} for {cfg.heads} heads")
+        self.n_freq = cfg.rot.dims // 2 if cfg.rot is not None else 0
+        self.freq = (torch.tensor([cfg.rot.base ** (-2.0 * i / cfg.rot.dims) for i in range(self.n_freq)], dtype=torch.float64, device=device)
+                     if self.n_freq else None)
+        self.opts = ops.attention_options(cfg.mask.size, cfg.mask.keep_first, cross_values=True)
+        self.out = FusedLinear([(w[pre + "o"], w.get(pre + "o.b"))], ops, device)
+        self.width = cfg.heads * cfg.vdim
+
+    def state_spec(self):
+        c = self.cfg
+        slots = [("ring", (c.conv - 1, self.channels))] if c.conv > 1 else []
+        return {"pages": [("k", c.kv_heads, c.dim), ("v", c.kv_heads, c.vdim)], "slots": slots}
+
+    def forward(self, step, cols, ld, state, out):
+        c, ops, T, C = self.cfg, self.ops, step.T, self.channels
+        H, G, dk, dv = c.heads, c.kv_heads, c.dim, c.vdim
+        raw = cols[0]
+        ring = state.get("ring")
+        u = step.scratch("talk_qk", T * C)
+        ops.conv_ring(step.b, raw, ld, C, c.conv, self.conv_w, ring, 0, u, C, step.st)
+        if ring is not None:
+            ops.ring_store(step.b, raw, ld, C, c.conv, ring, step.st)
+        q, k = u.data_ptr(), u.data_ptr() + self.nq * F32B
+        ops.normed_rotary_kv(step.b, q, C, H, dk, k, C, G, k, C, dv, self.q_norm, self.k_norm, self.eps, self.freq, self.n_freq, 0, state["k"], state["v"],
+                             step.st)
+        ws = step.scratch("attn_ws", T * H * G * step.nsplit * (dv + 2))
+        ops.attention(step.b, q, C, H, G, dk, dv, c.scale, state["k"], state["v"], step.nsplit, ws, step.st, opts=self.opts)
+        cross = step.scratch("talk_cross", T * G * H * dv)
+        ops.attention_finish(step.b, ws, step.nsplit, G * H, dv, None, 0, None, 0, cross, G * H * dv, step.st)
+        rows16 = self.out.operand_rows(step)
+        ops.head_mix(cross, G * H * dv, self.talk, H, G, dv, None if rows16 is not None else out, self.width, T, step.st, out16=rows16)
+        return rows16 is not None
+
+
 class MixerGroup:
     """One or more mechanisms reading the same input: their input projections run as one fused product, each mechanism's result goes
     through its own output projection, and the results are added with the given weights."""
@@ -455,6 +622,28 @@ class GatedFeedForward:
         self.down(step, act.data_ptr(), n, y.data_ptr(), self.down.N, a16_ready=rows16 is not None)
 
 
+class BiasedFeedForward:
+    """W_down act(W_up h + b_up) + b_down with act one of the framework's activations (0 = the exact, erf, gelu)."""
+
+    def __init__(self, cfg, w, pre, ops, device, activation=0):
+        self.ops, self.activation = ops, activation
+        self.up = FusedLinear([(w[pre + "up"], w.get(pre + "up.b"))], ops, device)
+        self.down = FusedLinear([(w[pre + "down"], w.get(pre + "down.b"))], ops, device)
+        if self.up.N != cfg.ff:
+            raise ValueError(f"{pre}up has {self.up.N} rows, the configuration says {cfg.ff}")
+
+    @property
+    def proj(self):
+        return self.up
+
+    def forward(self, step, h, y, h16_ready=False):
+        T, n = step.T, self.up.N
+        z = step.scratch("ff_z", T * n)
+        self.up(step, h.data_ptr(), self.up.K, z.data_ptr(), n, a16_ready=h16_ready)
+        self.ops.act(z.data_ptr(), T * n, self.activation, step.st)
+        self.down(step, z.data_ptr(), n, y.data_ptr(), self.down.N)
+
+
 class ExpertsFeedForward:
     """Mixture of experts W_down,e act(W_up,e h) (tensors ``e<i>.up`` / ``e<i>.down``, no biases): router logits W_router h in fp32,
     scores = softmax over ALL router outputs, the ``top`` largest (score + ``correction``) are chosen, the weights are the chosen scores
@@ -470,6 +659,7 @@ class ExpertsFeedForward:
     matrix, chosen on the device. All forms give the same numbers up to where the score is multiplied in."""
 
     activation = 0          # the exact (erf) gelu
+    GATED, SCALE_INPUT, SIGMOID = 4, 8, 16      # SLLM_MOE_* bits beside the activation
     # The gathered form trades arithmetic for launches (two products per expert): it is taken when the products it saves, at the rate the
     # tensor-core product sustains, outweigh what its launches cost (both measured on B200: small experts are faster computed densely).
     gather_min_tokens = 256
@@ -479,17 +669,25 @@ class ExpertsFeedForward:
     index_launch_cost = 12e-6      # seconds for the three extra launches of a step replayed as a graph
     index_stream_rate = 5e12       # bytes per second the weight-streaming body sustains
 
-    def __init__(self, cfg, w, pre, ops, device):
+    def __init__(self, cfg, w, pre, ops, device, activation=None, gated=False, sigmoid_scores=False, scale_input=False):
+        """``gated``: experts W_down (act(W_gate h) * (W_up h)) with tensors ``e<i>.gate`` beside ``up`` / ``down``; ``sigmoid_scores``: the score
+        of a router output is its own sigmoid (no softmax over all); ``scale_input``: the score multiplies what the expert reads."""
         self.cfg, self.ops = cfg, ops
         E = cfg.experts
+        self.gated, self.scale_input = bool(gated), bool(scale_input)
+        act = self.activation if activation is None else activation
+        self.mode = act | (self.GATED if gated else 0) | (self.SCALE_INPUT if scale_input else 0) | (self.SIGMOID if sigmoid_scores else 0)
+        self.ff_up = (2 if gated else 1) * cfg.ff          # columns of one expert's first product: [gate | up] or up
         self.n_route = E + cfg.identity
         if int(w[pre + "router"].shape[0]) != self.n_route:
             raise ValueError(f"{pre}router has {int(w[pre + 'router'].shape[0])} outputs, the configuration names {self.n_route} experts")
         self.correction = w[pre + "correction"].float().contiguous() if pre + "correction" in w else None
         # experts first, router last: the experts' columns then start at a 16-byte boundary for every ff
-        self.up = FusedLinear([(w[f"{pre}e{e}.up"], None) for e in range(E)] + [(w[pre + "router"], None)], ops, device, pad_rows=8)
+        first = [torch.cat([w[f"{pre}e{e}.gate"], w[f"{pre}e{e}.up"]], dim=0) if gated else w[f"{pre}e{e}.up"] for e in range(E)]
+        self.up = FusedLinear([(m, None) for m in first] + [(w[pre + "router"], None)], ops, device, pad_rows=8)
         self.down = FusedLinear([(torch.cat([w[f"{pre}e{e}.down"] for e in range(E)], dim=1).contiguous(), None)], ops, device)
-        self.wide = E * cfg.ff
+        self.wide = E * cfg.ff                     # columns of the activation = rows of the concatenated down matrices
+        self.wide_up = E * self.ff_up              # columns of all experts' first products; the router's follow
         # the gathered form: the router as a product of its own, the down matrices one behind the other [E][d][ff]
         self.gathers = cfg.top < self.n_route and E > 0
         if self.gathers:
@@ -502,7 +700,7 @@ class ExpertsFeedForward:
 
     def _forward_gathered(self, step, h, y, h16_ready=False):
         c, ops, T, d, st = self.cfg, self.ops, step.T, self.up.K, step.st
-        E, top, ff, cap = c.experts, c.top, c.ff, step.T
+        E, top, ff, cap, fu = c.experts, c.top, c.ff, step.T, self.ff_up
         ldl = self.router.N
         logits = step.scratch("moe_logits", T * ldl)
         self.router(step, h.data_ptr(), d, logits.data_ptr(), ldl, a16_ready=h16_ready)     # the bf16 rows left for the up product serve this one
@@ -510,22 +708,22 @@ class ExpertsFeedForward:
         book = step.scratch("moe_book", E + 3 * T * top + T).data_ptr()
         counts, sel_e, sel_pos, sel_w, ident = book, book + 4 * E, book + 4 * (E + T * top), book + 4 * (E + 2 * T * top), book + 4 * (E + 3 * T * top)
         # operands of the tensor-core products are gathered as bf16 rows; shapes its tiles do not take (and the fp32 mode) gather fp32 rows
-        tc = (step.gemm_scratch(d, ff) is not None and ops.on_tensor_cores(cap, ff, d) and ops.on_tensor_cores(cap, d, ff)
+        tc = (step.gemm_scratch(d, fu) is not None and ops.on_tensor_cores(cap, fu, d) and ops.on_tensor_cores(cap, d, ff)
               and self.up.w.data_ptr() % 16 == 0 and self.down_each.data_ptr() % 16 == 0)
         per = 2 if tc else 1                       # operand elements per float of scratch
         rows = step.scratch("moe_rows", -(-E * cap * d // per)).data_ptr()
-        up_out = step.scratch("moe_up", E * cap * ff).data_ptr()
+        up_out = step.scratch("moe_up", E * cap * fu).data_ptr()
         act = step.scratch("moe_act", -(-E * cap * ff // per)).data_ptr()
         down_out = step.scratch("moe_down", E * cap * d).data_ptr()
         ops.zero(counts, 4 * E, st)
         ops.moe_route(logits.data_ptr(), ldl, self.n_route, E, top, self.correction, h, d, d, counts, cap, sel_e, sel_pos, sel_w, ident,
-                      rows if tc else None, None if tc else rows, T, st)
+                      rows if tc else None, None if tc else rows, T, st, mode=self.mode)
         wb = self.up.w.element_size()
         for e in range(E):
             a = rows + e * cap * d * (2 if tc else 4)
-            ops.linear(a, d, self.up.w, d, None, up_out + 4 * e * cap * ff, ff, cap, ff, d, st, scratch=a if tc else None, a16_ready=tc, rows_dev=counts + 4 * e,
-                       w_ptr=self.up.w.data_ptr() + e * ff * d * wb)
-        ops.moe_expert_act(up_out, counts, E, cap, ff, self.activation, act if tc else None, None if tc else act, st)
+            ops.linear(a, d, self.up.w, d, None, up_out + 4 * e * cap * fu, fu, cap, fu, d, st, scratch=a if tc else None, a16_ready=tc, rows_dev=counts + 4 * e,
+                       w_ptr=self.up.w.data_ptr() + e * fu * d * wb)
+        ops.moe_expert_act(up_out, counts, E, cap, ff, self.mode, act if tc else None, None if tc else act, st)
         for e in range(E):
             a = act + e * cap * ff * (2 if tc else 4)
             ops.linear(a, ff, self.down_each, ff, None, down_out + 4 * e * cap * d, d, cap, d, ff, st, scratch=a if tc else None, a16_ready=tc,
@@ -534,14 +732,15 @@ class ExpertsFeedForward:
 
     def _gathered_pays(self, T: int) -> bool:
         c = self.cfg
-        saved = 4.0 * T * c.ff * self.up.K * (c.experts - min(c.top, c.experts)) / self.gather_product_rate
+        saved = 2.0 * T * (c.ff + self.ff_up) * self.up.K * (c.experts - min(c.top, c.experts)) / self.gather_product_rate
         return self.gathers and T >= self.gather_min_tokens and saved > 2 * c.experts * self.gather_launch_cost
 
     def _indexed_pays(self, T: int) -> bool:
         c = self.cfg
         pairs = T * c.top
         saved = (c.experts - pairs) * 2.0 * c.ff * self.up.K * self.up.w.element_size() / self.index_stream_rate
-        return self.gathers and T <= 8 and pairs < c.experts and saved > self.index_launch_cost
+        # (the indexed products read the token's row as it is: a score on the expert's input, or a gate beside the up product, is not in them)
+        return self.gathers and not (self.scale_input or self.gated) and T <= 8 and pairs < c.experts and saved > self.index_launch_cost
 
     def _forward_indexed(self, step, h, y):
         c, ops, T, d, st = self.cfg, self.ops, step.T, self.up.K, step.st
@@ -551,11 +750,12 @@ class ExpertsFeedForward:
         self.router(step, h.data_ptr(), d, logits.data_ptr(), ldl)
         book = step.scratch("moe_book", E + 3 * pairs + T).data_ptr()       # as in the gathered form; the counters stay unused
         sel_e, sel_pos, sel_w, ident = book + 4 * E, book + 4 * (E + pairs), book + 4 * (E + 2 * pairs), book + 4 * (E + 3 * pairs)
-        ops.moe_route(logits.data_ptr(), ldl, self.n_route, E, top, self.correction, h, d, d, None, T, sel_e, sel_pos, sel_w, ident, None, None, T, st)
+        ops.moe_route(logits.data_ptr(), ldl, self.n_route, E, top, self.correction, h, d, d, None, T, sel_e, sel_pos, sel_w, ident, None, None, T, st,
+                      mode=self.mode)
         up_out = step.scratch("moe_up", pairs * ff).data_ptr()
         down_out = step.scratch("moe_down", pairs * d).data_ptr()
         ops.linear_indexed(h.data_ptr(), d, d, top, self.up.w, d, ff * d, sel_e, up_out, ff, ff, pairs, ff, d, st)
-        ops.act(up_out, pairs * ff, self.activation, st)
+        ops.act(up_out, pairs * ff, self.mode & 3, st)
         ops.linear_indexed(up_out, ff, ff, 1, self.down_each, ff, d * ff, sel_e, down_out, d, d, pairs, d, ff, st)
         # row (t, k) of down_out is pair t * top + k: the combine kernel's (expert, row) address with buffers of 0 rows
         ops.moe_combine(down_out, sel_e, sel_pos, sel_w, top, ident, h, d, 0, d, y, d, T, st)
@@ -570,6 +770,6 @@ class ExpertsFeedForward:
         self.up(step, h.data_ptr(), d, z.data_ptr(), N, a16_ready=h16_ready)
         rows16 = self.down.operand_rows(step)
         act = step.scratch("ff_act", T * self.wide)   # fp32 rows; not written when the product reads the bf16 rows
-        self.ops.moe_act(z.data_ptr() + self.wide * F32B, N, self.n_route, c.experts, c.top, self.correction, z.data_ptr(), N, c.ff, self.activation,
+        self.ops.moe_act(z.data_ptr() + self.wide_up * F32B, N, self.n_route, c.experts, c.top, self.correction, z.data_ptr(), N, c.ff, self.mode,
                          h, d, d, None if rows16 is not None else act, rows16, y, d, T, step.st)
         self.down(step, act.data_ptr(), self.wide, y.data_ptr(), d, accumulate=True, a16_ready=rows16 is not None)

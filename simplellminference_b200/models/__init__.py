@@ -3,11 +3,12 @@ command line, the trace replayer, the tests) uses to go from a model folder to a
 from __future__ import annotations
 
 from ..config import BF16, F32, read_model_config
+from .kodezen import KodezenModel
 from .munazen import MunazenModel
 from .sopetar import SopetarModel
 from .vasosun import VasosunModel
 
-MODEL_CLASSES = {"Munazen": MunazenModel, "Sopetar": SopetarModel, "Vasosun": VasosunModel}
+MODEL_CLASSES = {"Munazen": MunazenModel, "Sopetar": SopetarModel, "Vasosun": VasosunModel, "Kodezen": KodezenModel}
 
 
 def build_model(model_dir: str, dtype: str = "bfloat16", device="cuda", build: bool = False):

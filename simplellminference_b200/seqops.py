@@ -75,8 +75,10 @@ class Ops:
     def gather_rows(self, x, ldx, rows, n, d, out, st):
         self._ck(self.lib.sllm_seq_gather_rows(_p(x), ldx, _p(rows), n, d, _p(out), st))
 
-    def headnorm_gate(self, o_ptr, ldo, g_ptr, ldg, w, heads, dv, eps, out, ldout, T, st):
-        self._ck(self.lib.sllm_seq_headnorm_gate(o_ptr, ldo, g_ptr, ldg, _p(w), heads, dv, eps, _p(out), ldout, T, st))
+    def headnorm_gate(self, o_ptr, ldo, g_ptr, ldg, w, heads, dv, eps, out, ldout, T, st, out16=None, gate_first=False, wide_weight=False):
+        """``gate_first``: the gate multiplies before the norm; ``wide_weight``: w holds heads * dv entries instead of dv."""
+        self._ck(self.lib.sllm_seq_headnorm_gate(o_ptr, ldo, g_ptr, ldg, _p(w), heads, dv, eps, _p(out), ldout, _p(out16), T,
+                                                 int(bool(gate_first)) | 2 * int(bool(wide_weight)), st))
 
     # ---- attention over the paged cache ----
     def rotary_kv(self, b, q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, freq, n_freq, magnitude, vfreq, layout, k_pool, v_pool, st):
@@ -91,9 +93,17 @@ class Ops:
         self._ck(self.lib.sllm_seq_attention_finish(C.byref(b), _p(ws), nsplit, heads, dv, _p(vfreq), layout, gate_ptr, ldg, _p(sink), _p(out), ldo, st))
 
     @staticmethod
-    def attention_options(window=0, keep_first=0, softcap=0.0, slopes=None, values_in_keys=False, logdist=None):
+    def attention_options(window=0, keep_first=0, softcap=0.0, slopes=None, values_in_keys=False, logdist=None, cross_values=False):
         """The options structure of ``attention``; the caller keeps the ``slopes`` and ``logdist`` tensors alive."""
-        return _lib.SeqAttnOpts(int(window or 0), int(keep_first or 0), float(softcap or 0.0), _p(slopes), int(bool(values_in_keys)), _p(logdist))
+        return _lib.SeqAttnOpts(int(window or 0), int(keep_first or 0), float(softcap or 0.0), _p(slopes), int(bool(values_in_keys)), _p(logdist),
+                                int(bool(cross_values)))
+
+    def normed_rotary_kv(self, b, q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, q_norm_w, k_norm_w, eps, freq, n_freq, layout, k_pool, v_pool, st):
+        self._ck(self.lib.sllm_seq_normed_rotary_kv(C.byref(b), q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, _p(q_norm_w), _p(k_norm_w), eps,
+                                                    _p(freq), n_freq, layout, _p(k_pool), _p(v_pool), self.kv_dtype, st))
+
+    def head_mix(self, x, ldx, mix, heads, kv_heads, dv, out, ldo, T, st, out16=None):
+        self._ck(self.lib.sllm_seq_head_mix(_p(x), ldx, _p(mix), heads, kv_heads, dv, _p(out), ldo, _p(out16), T, st))
 
     def unit_kv(self, b, q_ptr, ldq, heads, dk, k_ptr, ldk, kv_heads, v_ptr, ldv, dv, eps, unit, v_shared, share, lam, k_pool, v_pool, st,
                 q_temp_coef=0.0, q_temp_every=0):
@@ -110,10 +120,11 @@ class Ops:
         self._ck(self.lib.sllm_seq_embed_pair(_p(ids), _p(prev_ids), _p(table), _p(pairs), self.w_dtype, vocab, d, buckets, mul_prev, mul_cur, _p(out), T, st))
 
     def seam(self, b, x_in, d, st, x_out=None, y=None, post_g=1.0, pre_g=None, eps=0.0, conv_w=None, taps=1, ring=None, h=None, h16=None, stash=None,
-             flush_ring=None, flush_taps=0, scales=None):
-        """x_out = x_in + post_g * y / rms(y) (if ``y``), then h = n + conv(n), n = pre_g * x / rms(x) (if ``pre_g`` is given)."""
+             flush_ring=None, flush_taps=0, scales=None, post_norm=True, pre_w=None, pre_w_offset=0.0):
+        """x_out = x_in + post_g * y / rms(y) (if ``y``; ``post_norm`` False: x_in + y), then h = n + conv(n), n = pre_g * x / rms(x) (if
+        ``pre_g`` is given), times (pre_w_offset + pre_w) per channel if ``pre_w`` is."""
         self._ck(self.lib.sllm_seq_seam(C.byref(b), _p(x_in), _p(x_out), _p(y), post_g, int(pre_g is not None), pre_g or 0.0, eps, _p(conv_w), taps, _p(ring),
-                                        _p(h), _p(h16), _p(stash), _p(flush_ring), flush_taps, d, _p(scales), st))
+                                        _p(h), _p(h16), _p(stash), _p(flush_ring), flush_taps, d, _p(scales), int(bool(post_norm)), _p(pre_w), pre_w_offset, st))
 
     def rmsnorm_rows(self, x_ptr, ldx, w, eps, y_ptr, ldy, T, n, st):
         self._ck(self.lib.sllm_seq_rmsnorm_rows(x_ptr, ldx, _p(w), eps, y_ptr, ldy, T, n, st))
@@ -132,9 +143,10 @@ class Ops:
     def zero(self, ptr, n_bytes, st):
         self._ck(self.lib.sllm_seq_zero(ptr, n_bytes, st))
 
-    def moe_route(self, logits_ptr, ldl, n_route, experts, top, correction, h, ldh, d, counts_ptr, cap, sel_e, sel_pos, sel_w, ident, rows16, rows32, T, st):
+    def moe_route(self, logits_ptr, ldl, n_route, experts, top, correction, h, ldh, d, counts_ptr, cap, sel_e, sel_pos, sel_w, ident, rows16, rows32, T, st,
+                  mode=0):
         self._ck(self.lib.sllm_seq_moe_route(logits_ptr, ldl, n_route, experts, top, _p(correction), _p(h), ldh, d, counts_ptr, cap, sel_e, sel_pos, sel_w, ident,
-                                             rows16, rows32, T, st))
+                                             rows16, rows32, T, mode, st))
 
     def act(self, x_ptr, n, kind, st):
         self._ck(self.lib.sllm_seq_act(x_ptr, n, kind, st))
@@ -150,8 +162,21 @@ class Ops:
         self._ck(self.lib.sllm_seq_moe_combine(down_ptr, sel_e, sel_pos, sel_w, top, ident, _p(h), ldh, cap, d, _p(y), ldy, T, st))
 
     # ---- recurrences ----
-    def conv_ring(self, b, x_ptr, ldx, channels, taps, w, ring, act, out, ldo, st):
-        self._ck(self.lib.sllm_seq_conv_ring(C.byref(b), x_ptr, ldx, channels, taps, _p(w), _p(ring), act, _p(out), ldo, st))
+    def conv_ring(self, b, x_ptr, ldx, channels, taps, w, ring, act, out, ldo, st, bias=None):
+        self._ck(self.lib.sllm_seq_conv_ring(C.byref(b), x_ptr, ldx, channels, taps, _p(w), _p(bias), _p(ring), act, _p(out), ldo, st))
+
+    def ring_store(self, b, x_ptr, ldx, channels, taps, ring, st):
+        self._ck(self.lib.sllm_seq_ring_store(C.byref(b), x_ptr, ldx, channels, taps, _p(ring), st))
+
+    def ssd_scan(self, b, x_ptr, ldx, B_ptr, ldb, C_ptr, ldc, step_ptr, lda, a_log, dt_bias, skip, heads, groups, n_state, dv, state, y, ldy, conv_x_ptr, ld_conv,
+                 channels, taps, ring, st):
+        self._ck(self.lib.sllm_seq_ssd_scan(C.byref(b), x_ptr, ldx, B_ptr, ldb, C_ptr, ldc, step_ptr, lda, _p(a_log), _p(dt_bias), _p(skip), heads, groups, n_state,
+                                            dv, _p(state), _p(y), ldy, conv_x_ptr, ld_conv, channels, taps, _p(ring), st))
+
+    def selective_scan(self, b, x_ptr, ldx, step_ptr, lddt, B_ptr, ldb, C_ptr, ldc, z_ptr, ldz, a_log, skip, inner, n_state, state, out, ldo, conv_x_ptr, ld_conv,
+                       taps, ring, st, out16=None):
+        self._ck(self.lib.sllm_seq_selective_scan(C.byref(b), x_ptr, ldx, step_ptr, lddt, B_ptr, ldb, C_ptr, ldc, z_ptr, ldz, _p(a_log), _p(skip), inner, n_state,
+                                                  _p(state), _p(out), ldo, _p(out16), conv_x_ptr, ld_conv, taps, _p(ring), st))
 
     def delta_rule(self, b, q_ptr, ldq, k_ptr, ldk, v_ptr, ldv, beta_ptr, ldb, step_ptr, lda, a_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale,
                    state, o, ldo, conv_x_ptr, ldx, channels, taps, ring, st):
