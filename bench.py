@@ -73,6 +73,10 @@ def parse():
                     help="instead of the headline workload: prefill and decode throughput of the Vasosun design (scalar-norm sublayers with an input convolution, "
                          "window / latent attention, gated delta rule, mixture of experts) beside Sopetar and the Llama engine at equal size; comma-separated "
                          "sizes of simplellminference_b200/bench_vasosun.py (w1024,w2048,w4096) or 'all'. One GPU; prints one JSON line {\"vasosun\": [...]}")
+    ap.add_argument("--kodezen", default=None, metavar="SIZES",
+                    help="instead of the headline workload: prefill and decode throughput of the Kodezen design (pre-norm layers behind an input convolution; "
+                         "Mamba-2, Mamba and talking-heads window attention; biased gelu and gated experts) beside the closest model (Vasosun) at equal width "
+                         "and depth, at the sizes of simplellminference_b200/bench_kodezen.py (w1024,w2048,w4096) or 'all'. One GPU; prints one JSON line {\"kodezen\": [...]}")
     ap.add_argument("--no-batch", action="store_true", help="(kept for old command lines: the secondary measurements are opt-in now, see --extras)")
     return ap.parse_args()
 
@@ -648,9 +652,12 @@ def main():
     real_stdout = os.dup(1)
     os.dup2(2, 1)
     sys.stdout = os.fdopen(real_stdout, "w", buffering=1)
-    if args.hybrid or args.sopetar or args.vasosun:
+    if args.hybrid or args.sopetar or args.vasosun or args.kodezen:
         import torch
-        if args.hybrid:
+        if args.kodezen:
+            from simplellminference_b200 import bench_kodezen as bench_hybrid
+            key, wanted = "kodezen", args.kodezen
+        elif args.hybrid:
             from simplellminference_b200 import bench_hybrid
             key, wanted = "hybrid", args.hybrid
         elif args.vasosun:

@@ -591,6 +591,10 @@ int sllm_seq_moe_route(const float* logits, int32_t ldl, int32_t n_route, int32_
                        void* rows16, float* rows32, int32_t T, int32_t act, sllm_stream_t stream);
 int sllm_seq_moe_expert_act(const float* up, const int32_t* counts, int32_t experts, int32_t cap, int32_t ff, int32_t act, void* out16,
                             float* out32, sllm_stream_t stream);
+/* For experts chosen on the device (rows in the order of the (token, choice) pairs, sel_w the pairs' scores as sllm_seq_moe_route leaves them
+ * WITHOUT SLLM_MOE_SCALE_INPUT): out [pairs][ff] = act(s * up) or, gated, act(s * gate) * (s * up) over up [pairs][ff or 2 ff], s = the score
+ * when `act` has SLLM_MOE_SCALE_INPUT and 1 otherwise; w_out [pairs] = the weight sllm_seq_moe_combine has to use (1, or the score). */
+int sllm_seq_moe_pair_act(const float* up, const float* sel_w, int32_t pairs, int32_t ff, int32_t act, float* out, float* w_out, sllm_stream_t stream);
 int sllm_seq_moe_combine(const float* down, const int32_t* sel_e, const int32_t* sel_pos, const float* sel_w, int32_t top, const float* ident,
                          const float* h, int32_t ldh, int32_t cap, int32_t d, float* y, int32_t ldy, int32_t T, sllm_stream_t stream);
 /* x <- act(x) over n floats (act as in sllm_seq_moe_act). With counts, rows16 and rows32 all NULL sllm_seq_moe_route only routes: nothing is

@@ -138,6 +138,7 @@ SIGNATURES.update({
     "sllm_seq_linear": (C.c_int, [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _L, _L, _L, _L, _P, _I, _P, _P]),
     "sllm_seq_moe_route": (C.c_int, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _P]),
     "sllm_seq_moe_expert_act": (C.c_int, [_P, _P, _I, _I, _I, _I, _P, _P, _P]),
+    "sllm_seq_moe_pair_act": (C.c_int, [_P, _P, _I, _I, _I, _P, _P, _P]),
     "sllm_seq_moe_combine": (C.c_int, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _I, _I, _P]),
     "sllm_seq_zero": (C.c_int, [_P, _L, _P]),
     "sllm_seq_act": (C.c_int, [_P, _L, _I, _P]),

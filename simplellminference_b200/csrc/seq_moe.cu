@@ -236,6 +236,20 @@ __global__ void seq_moe_expert_act_kernel(const float* __restrict__ up, const in
     }
 }
 
+// one CTA per (token, choice) pair, rows in the pairs' own order: out = act(s * up) or act(s * gate) * (s * up), with s the pair's score when
+// the score multiplies what the expert reads (the products are linear: the score is applied to their results) and 1 otherwise;
+// w_out takes what the combine kernel has to multiply the pair's down row by: 1 in the first case, the score in the second
+__global__ void seq_moe_pair_act_kernel(const float* __restrict__ up, const float* __restrict__ sel_w, int ff, int act, float* __restrict__ out,
+                                        float* __restrict__ w_out) {
+    const int p = blockIdx.x;
+    const bool gated = act & kMoeGated, on_input = act & kMoeScaleInput;
+    const float score = sel_w[p], s = on_input ? score : 1.0f;
+    const float* row = up + (size_t)p * ff * (gated ? 2 : 1);
+    for (int j = threadIdx.x; j < ff; j += blockDim.x)
+        out[(size_t)p * ff + j] = gated ? moe_act(s * row[j], act) * (s * row[ff + j]) : moe_act(s * row[j], act);
+    if (threadIdx.x == 0) w_out[p] = on_input ? 1.0f : score;
+}
+
 __global__ void seq_moe_combine_kernel(const float* __restrict__ down, const int32_t* __restrict__ sel_e, const int32_t* __restrict__ sel_pos,
                                        const float* __restrict__ sel_w, int top, const float* __restrict__ ident, const float* __restrict__ h, int ldh,
                                        int cap, int d, float* __restrict__ y, int ldy) {
@@ -297,6 +311,14 @@ int sllm_seq_moe_expert_act(const float* up, const int32_t* counts, int32_t expe
     SLLM_REQUIRE(up && counts && (out16 || out32) && experts > 0 && cap > 0 && cap <= 65535 * 32 && ff > 0 && act >= 0 && (act & 3) <= 2, SLLM_EINVAL, "seq_moe_expert_act: bad argument");
     SLLM_REQUIRE(experts <= 65535, SLLM_ENOTSUP, "seq_moe_expert_act: %d experts", experts);
     seq_moe_expert_act_kernel<<<dim3(cap, experts), 256, 0, as_stream(stream)>>>(up, counts, cap, ff, act, (uint16_t*)out16, out32);
+    ++g_launches;
+    SLLM_LAUNCH_CHECK();
+    return SLLM_OK;
+}
+
+int sllm_seq_moe_pair_act(const float* up, const float* sel_w, int32_t pairs, int32_t ff, int32_t act, float* out, float* w_out, sllm_stream_t stream) {
+    SLLM_REQUIRE(up && sel_w && out && w_out && pairs > 0 && ff > 0 && act >= 0 && (act & 3) <= 2 && act < 32, SLLM_EINVAL, "seq_moe_pair_act: bad argument");
+    seq_moe_pair_act_kernel<<<pairs, 256, 0, as_stream(stream)>>>(up, sel_w, ff, act, out, w_out);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

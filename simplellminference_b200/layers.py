@@ -738,27 +738,34 @@ class ExpertsFeedForward:
     def _indexed_pays(self, T: int) -> bool:
         c = self.cfg
         pairs = T * c.top
-        saved = (c.experts - pairs) * 2.0 * c.ff * self.up.K * self.up.w.element_size() / self.index_stream_rate
-        # (the indexed products read the token's row as it is: a score on the expert's input, or a gate beside the up product, is not in them)
-        return self.gathers and not (self.scale_input or self.gated) and T <= 8 and pairs < c.experts and saved > self.index_launch_cost
+        saved = (c.experts - pairs) * float(c.ff + self.ff_up) * self.up.K * self.up.w.element_size() / self.index_stream_rate
+        return self.gathers and T <= 8 and pairs < c.experts and saved > self.index_launch_cost
 
     def _forward_indexed(self, step, h, y):
         c, ops, T, d, st = self.cfg, self.ops, step.T, self.up.K, step.st
-        E, top, ff = c.experts, c.top, c.ff
+        E, top, ff, fu = c.experts, c.top, c.ff, self.ff_up
         pairs, ldl = T * top, self.router.N
         logits = step.scratch("moe_logits", T * ldl)
         self.router(step, h.data_ptr(), d, logits.data_ptr(), ldl)
         book = step.scratch("moe_book", E + 3 * pairs + T).data_ptr()       # as in the gathered form; the counters stay unused
         sel_e, sel_pos, sel_w, ident = book + 4 * E, book + 4 * (E + pairs), book + 4 * (E + 2 * pairs), book + 4 * (E + 3 * pairs)
+        # the products read the token's row as it is; a score on the expert's input is applied to their results (they are linear), so the
+        # routing kernel is asked for the plain scores
         ops.moe_route(logits.data_ptr(), ldl, self.n_route, E, top, self.correction, h, d, d, None, T, sel_e, sel_pos, sel_w, ident, None, None, T, st,
-                      mode=self.mode)
-        up_out = step.scratch("moe_up", pairs * ff).data_ptr()
+                      mode=self.mode & ~self.SCALE_INPUT)
+        up_out = step.scratch("moe_up", pairs * fu).data_ptr()
         down_out = step.scratch("moe_down", pairs * d).data_ptr()
-        ops.linear_indexed(h.data_ptr(), d, d, top, self.up.w, d, ff * d, sel_e, up_out, ff, ff, pairs, ff, d, st)
-        ops.act(up_out, pairs * ff, self.mode & 3, st)
-        ops.linear_indexed(up_out, ff, ff, 1, self.down_each, ff, d * ff, sel_e, down_out, d, d, pairs, d, ff, st)
+        ops.linear_indexed(h.data_ptr(), d, d, top, self.up.w, d, fu * d, sel_e, up_out, fu, fu, pairs, fu, d, st)
+        if self.gated or self.scale_input:
+            act = step.scratch("moe_act", pairs * ff).data_ptr()
+            weights = step.scratch("moe_pair_w", pairs).data_ptr()
+            ops.moe_pair_act(up_out, sel_w, pairs, ff, self.mode, act, weights, st)
+        else:
+            ops.act(up_out, pairs * ff, self.mode & 3, st)
+            act, weights = up_out, sel_w
+        ops.linear_indexed(act, ff, ff, 1, self.down_each, ff, d * ff, sel_e, down_out, d, d, pairs, d, ff, st)
         # row (t, k) of down_out is pair t * top + k: the combine kernel's (expert, row) address with buffers of 0 rows
-        ops.moe_combine(down_out, sel_e, sel_pos, sel_w, top, ident, h, d, 0, d, y, d, T, st)
+        ops.moe_combine(down_out, sel_e, sel_pos, weights, top, ident, h, d, 0, d, y, d, T, st)
 
     def forward(self, step, h, y, h16_ready=False):
         if self._gathered_pays(step.T):

@@ -158,6 +158,9 @@ class Ops:
     def moe_expert_act(self, up_ptr, counts_ptr, experts, cap, ff, act, out16, out32, st):
         self._ck(self.lib.sllm_seq_moe_expert_act(up_ptr, counts_ptr, experts, cap, ff, act, out16, out32, st))
 
+    def moe_pair_act(self, up_ptr, sel_w_ptr, pairs, ff, act, out_ptr, w_out_ptr, st):
+        self._ck(self.lib.sllm_seq_moe_pair_act(up_ptr, sel_w_ptr, pairs, ff, act, out_ptr, w_out_ptr, st))
+
     def moe_combine(self, down_ptr, sel_e, sel_pos, sel_w, top, ident, h, ldh, cap, d, y, ldy, T, st):
         self._ck(self.lib.sllm_seq_moe_combine(down_ptr, sel_e, sel_pos, sel_w, top, ident, _p(h), ldh, cap, d, _p(y), ldy, T, st))
 

@@ -387,6 +387,27 @@ def test_experts_with_the_tokens_gathered_per_expert(dtype, monkeypatch):
         assert _rel(gathered, want) < tol and _rel(every, want) < tol, (mlp, _rel(gathered, want), _rel(every, want))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_experts_chosen_on_the_device_in_steps_of_few_tokens(dtype, monkeypatch):
+    """Decoding steps stream only the chosen experts' matrices (one launch for all first products, one for all second ones); the score on
+    the expert's input is applied to the results of the first products. The same numbers as the form that computes every expert."""
+    from simplellminference_b200 import layers
+    rng, d = np.random.default_rng(15), 64
+    for mlp, T in ((L.moe(experts=12, top=2, ff=32), 3), (L.moe(experts=9, top=1, ff=24), 8), (L.moe(experts=7, top=3, ff=20), 2), (L.moe(experts=5, top=4, ff=8), 1)):
+        w = L.random_weights(L.make_config([L.mamba2_layer(mlp=mlp)], width=d), seed=6)
+        stub, ff = _ff_stub(mlp, w, d, dtype)
+        h = L.bf16_round(2 * rng.standard_normal((T, d))).astype(np.float32)
+        monkeypatch.setattr(layers.ExpertsFeedForward, "index_launch_cost", 1e9)
+        assert not ff._indexed_pays(T)
+        every = L.feed(stub, h, [T])[0]
+        monkeypatch.setattr(layers.ExpertsFeedForward, "index_launch_cost", 0.0)
+        assert ff._indexed_pays(T)
+        indexed = L.feed(stub, h, [T])[0]
+        want = _oracle_ff(mlp, w, h)
+        tol = F32_TOL if dtype == "float32" else BF16_MIXER
+        assert _rel(indexed, want) < tol and _rel(every, want) < tol, (mlp, _rel(indexed, want), _rel(every, want))
+
+
 # ------------------------------------------------------------------------------------------------ whole models
 @pytest.mark.parametrize("cfg", ALL, ids=IDS)
 def test_whole_prompt_matches_oracle_fp32_and_layers(tmp_path, cfg):
