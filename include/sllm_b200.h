@@ -549,11 +549,13 @@ int sllm_seq_ssd_scan(const sllm_seq_batch* b, const float* x, int32_t ldx, cons
 /* Selective scan (Mamba) per channel c over each sequence, state [slots][inner][n_state] fp32: dt = softplus(step_logit[c]),
  * S[c][n] <- exp(-dt exp(A_log[c][n])) S[c][n] + dt x[c] B[n], y[c] = sum_n S[c][n] C[n] + D[c] x[c], out = y * silu(z); B and C [T][n_state]
  * are shared by the channels. out fp32 [T][ldo] and / or out16 dense bf16 [T][inner]. ring (or NULL): the last taps-1 rows of conv_x
- * [T][inner] of every portion are stored there for the convolution of the next step. n_state <= 128. */
+ * [T][inner] of every portion are stored there for the convolution of the next step. n_state <= 128. scratch (NULL = always token by token):
+ * n_qtiles * inner * (n_state + 1) floats; with it, steps that hold a portion longer than 128 tokens run as three passes over ranges of 128
+ * tokens (every range from zero, a carry per state element, every range again from its start state). */
 int sllm_seq_selective_scan(const sllm_seq_batch* b, const float* x, int32_t ldx, const float* step_logit, int32_t lddt, const float* B, int32_t ldb,
                             const float* C, int32_t ldc, const float* z, int32_t ldz, const float* A_log, const float* D, int32_t inner,
                             int32_t n_state, float* state, float* out, int32_t ldo, void* out16, const float* conv_x, int32_t ld_conv, int32_t taps,
-                            float* ring, sllm_stream_t stream);
+                            float* ring, float* scratch, sllm_stream_t stream);
 /* Query and key heads RMS-normed over their dk dimensions with a weight [dk] shared by the heads (q_norm_w / k_norm_w, NULL = that kind
  * is not normed), then their first 2*n_freq dimensions turned by pos * freq[i] (layout and angles as in sllm_seq_rotary_kv); q in place,
  * k to its pool; v [T][kv_heads * dv] goes to its pool as it is (it may be k itself: values that are the keys before norm and rotation). */

@@ -5,12 +5,18 @@
 // enters the recurrence is fp32. The channels are independent recurrences that share B and C: a CTA takes 32 channels of one portion,
 // eight adjacent lanes own the states of one channel in registers (lane l holds states l, l + 8, ...) and meet by shuffles; the tokens
 // of a portion are staged in shared memory a chunk at a time and walked in order.
+//
+// The recurrence is linear in the state, with a decay whose product over a run of tokens is exp(A * (sum of the run's dt)). Steps that hold
+// a long portion therefore run as three passes over ranges of kScanRange tokens: (1) every range, in parallel, from a zero state: its end
+// state Q and its sum of dt; (2) per state element, the ranges of a portion in order: start of range r+1 = exp(A * sum_r) * start_r + Q_r,
+// the last one being the sequence's new state; (3) every range again, in parallel, from its start state, writing the outputs.
 #include "seq_common.cuh"
 
 namespace sllm {
 
 constexpr int kScanLanes = 8;       // lanes that share a channel's states
 constexpr int kScanChannels = 32;   // channels of a CTA (256 threads)
+constexpr int kScanRange = 128;     // tokens of a range of the three-pass form (four query tiles of the batch description)
 
 struct ScanArgs {
     sllm_seq_batch b;
@@ -21,29 +27,39 @@ struct ScanArgs {
     float* out; int ldo; uint16_t* out16;                               // [T][inner] fp32 and / or dense bf16 rows
     const float* conv_x; int ld_conv, taps; float* ring;                // the convolution's inputs [T][inner] -> ring [slots][taps-1][inner]
     int chunk;
+    float* ws; int nrange;                                              // three passes: per range [inner][N] states, then [inner] sums of dt
 };
 
-template <int R>   // states per lane: N <= 8 * R
+// where range `rg` of segment `seg` keeps its summary: ranges are numbered by the first query tile (32 tokens) of the segment
+__device__ __forceinline__ size_t scan_range_id(const sllm_seq_batch& b, int seg, int rg) { return (size_t)b.seg_tile0[seg] + rg; }
+
+// R: states per lane, N <= 8 * R. MODE 0: a CTA walks a whole portion from the sequence's state and stores the state back; MODE 1: a range
+// from zero, leaving its end state and its sum of dt in the workspace; MODE 2: a range from the start state the carry kernel left there.
+template <int R, int MODE>
 __global__ void __launch_bounds__(kScanLanes * kScanChannels) seq_selective_scan_kernel(ScanArgs p) {
     extern __shared__ __align__(16) float ssm_sm[];
     const sllm_seq_batch& b = p.b;
-    const int seg = blockIdx.x, c0 = blockIdx.y * kScanChannels;
-    const int start = b.seg_start[seg], len = b.seg_len[seg], slot = b.seg_slot[seg], pos0 = b.seg_pos0[seg];
+    const int seg = MODE == 0 ? blockIdx.x : blockIdx.x / p.nrange, rg = MODE == 0 ? 0 : blockIdx.x % p.nrange, c0 = blockIdx.y * kScanChannels;
+    const int seg_len = b.seg_len[seg], r0 = rg * kScanRange;
+    if (MODE != 0 && r0 >= seg_len) return;
+    const int start = b.seg_start[seg] + r0, len = MODE == 0 ? seg_len : min(kScanRange, seg_len - r0), slot = b.seg_slot[seg];
     const int N = p.N, C = p.chunk;
     const int cl = threadIdx.x / kScanLanes, sub = threadIdx.x % kScanLanes, c = c0 + cl;
     const bool live = c < p.inner;
     // per staged token: B [N], C [N], then dt, x, z and the result of the CTA's channels
     const int per_tok = 2 * N + 4 * kScanChannels;
     float A[R], S[R];
-    float* st = p.state + ((size_t)slot * p.inner + (live ? c : 0)) * N;
+    float* st = MODE == 0 ? p.state + ((size_t)slot * p.inner + (live ? c : 0)) * N
+                          : p.ws + (scan_range_id(b, seg, rg) * p.inner + (live ? c : 0)) * N;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int n = sub + r * kScanLanes;
         const bool has = live && n < N;
         A[r] = has ? -expf(p.A_log[(size_t)c * N + n]) : 0.0f;
-        S[r] = has ? st[n] : 0.0f;
+        S[r] = (has && MODE != 1) ? st[n] : 0.0f;
     }
     const float skip = live ? p.D[c] : 0.0f;
+    float dt_sum = 0.0f;
     for (int t0 = 0; t0 < len; t0 += C) {
         const int n_tok = min(C, len - t0);
         __syncthreads();                                   // everyone has left the chunk before
@@ -59,7 +75,7 @@ __global__ void __launch_bounds__(kScanLanes * kScanChannels) seq_selective_scan
             float* row = ssm_sm + tok * per_tok + 2 * N;
             row[ch] = ok ? seq_softplus(p.dtl[t * p.lddt + c0 + ch]) : 0.0f;
             row[kScanChannels + ch] = ok ? p.x[t * p.ldx + c0 + ch] : 0.0f;
-            row[2 * kScanChannels + ch] = ok ? p.z[t * p.ldz + c0 + ch] : 0.0f;
+            if (MODE != 1) row[2 * kScanChannels + ch] = ok ? p.z[t * p.ldz + c0 + ch] : 0.0f;
         }
         __syncthreads();
         for (int i = 0; i < n_tok; ++i) {
@@ -69,6 +85,15 @@ __global__ void __launch_bounds__(kScanLanes * kScanChannels) seq_selective_scan
             const float dt = row[cl], xv = row[kScanChannels + cl];
             const float dx = dt * xv;
             float acc = 0.0f;
+            if (MODE == 1) {                               // the end state only
+                dt_sum += dt;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int n = sub + r * kScanLanes;
+                    if (n < N) S[r] = fmaf(expf(dt * A[r]), S[r], dx * sB[n]);
+                }
+                continue;
+            }
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const int n = sub + r * kScanLanes;
@@ -85,6 +110,7 @@ __global__ void __launch_bounds__(kScanLanes * kScanChannels) seq_selective_scan
             }
         }
         __syncthreads();
+        if (MODE != 1)
         for (int i = threadIdx.x; i < n_tok * kScanChannels; i += blockDim.x) {
             const int tok = i / kScanChannels, ch = i % kScanChannels;
             if (c0 + ch >= p.inner) continue;
@@ -94,18 +120,45 @@ __global__ void __launch_bounds__(kScanLanes * kScanChannels) seq_selective_scan
             if (p.out16) p.out16[t * p.inner + c0 + ch] = f32_to_bf16_bits(v);
         }
     }
+    if (MODE != 2) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int n = sub + r * kScanLanes;
-        if (live && n < N) st[n] = S[r];
-    }
-    if (p.ring && p.taps > 1) {           // the portion's last inputs of the convolution, this CTA's channels
-        const int keep = min(len, p.taps - 1);
-        for (int i = threadIdx.x; i < keep * kScanChannels; i += blockDim.x) {
-            const int r = len - keep + i / kScanChannels, ch = c0 + i % kScanChannels;
-            if (ch < p.inner) p.ring[((size_t)slot * (p.taps - 1) + (pos0 + r) % (p.taps - 1)) * p.inner + ch] = p.conv_x[(size_t)(start + r) * p.ld_conv + ch];
+        for (int r = 0; r < R; ++r) {
+            const int n = sub + r * kScanLanes;
+            if (live && n < N) st[n] = S[r];
         }
     }
+    if (MODE == 1 && live && sub == 0) p.ws[(size_t)b.n_qtiles * p.inner * N + scan_range_id(b, seg, rg) * p.inner + c] = dt_sum;
+    if (MODE != 1 && p.ring && p.taps > 1 && r0 + len == seg_len) {           // the portion's last inputs of the convolution, this CTA's channels
+        const int seg_start = b.seg_start[seg], pos0 = b.seg_pos0[seg];
+        const int keep = min(seg_len, p.taps - 1);
+        for (int i = threadIdx.x; i < keep * kScanChannels; i += blockDim.x) {
+            const int r = seg_len - keep + i / kScanChannels, ch = c0 + i % kScanChannels;
+            if (ch < p.inner) p.ring[((size_t)slot * (p.taps - 1) + (pos0 + r) % (p.taps - 1)) * p.inner + ch] = p.conv_x[(size_t)(seg_start + r) * p.ld_conv + ch];
+        }
+    }
+}
+
+// thread = one state element (channel c, state n) of one portion: its ranges in order, end state from zero -> start state; the last
+// start state, moved on over the last range, is the sequence's new state
+__global__ void seq_selective_scan_carry_kernel(ScanArgs p) {
+    const sllm_seq_batch& b = p.b;
+    const int seg = blockIdx.y;
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x, per = (size_t)p.inner * p.N;
+    if (e >= per) return;
+    const int c = (int)(e / p.N);
+    const int ranges = (b.seg_len[seg] + kScanRange - 1) / kScanRange;
+    const float A = -expf(p.A_log[e]);
+    float* sp = p.state + (size_t)b.seg_slot[seg] * per + e;
+    const float* sums = p.ws + (size_t)b.n_qtiles * per;
+    float S = *sp;
+    for (int rg = 0; rg < ranges; ++rg) {
+        const size_t id = scan_range_id(b, seg, rg);
+        float* qp = p.ws + id * per + e;
+        const float Q = *qp;
+        *qp = S;
+        S = fmaf(expf(A * sums[id * p.inner + c]), S, Q);
+    }
+    *sp = S;
 }
 
 // ring[slot][p % (taps-1)][c] <- x[t][c] for the last taps-1 tokens of every portion (position p); grid (nseg, blocks of channels)
@@ -128,7 +181,7 @@ extern "C" {
 int sllm_seq_selective_scan(const sllm_seq_batch* b, const float* x, int32_t ldx, const float* step_logit, int32_t lddt, const float* B, int32_t ldb,
                             const float* C, int32_t ldc, const float* z, int32_t ldz, const float* A_log, const float* D, int32_t inner, int32_t n_state,
                             float* state, float* out, int32_t ldo, void* out16, const float* conv_x, int32_t ld_conv, int32_t taps, float* ring,
-                            sllm_stream_t stream) {
+                            float* scratch, sllm_stream_t stream) {
     SLLM_REQUIRE(b && b->T > 0 && b->nseg > 0 && b->seg_start && b->seg_len && b->seg_slot && b->seg_pos0, SLLM_EINVAL, "seq_selective_scan: incomplete batch description");
     SLLM_REQUIRE(x && step_logit && B && C && z && A_log && D && state && (out || out16) && inner > 0 && n_state > 0, SLLM_EINVAL, "seq_selective_scan: bad argument");
     SLLM_REQUIRE(!ring || (conv_x && taps >= 1), SLLM_EINVAL, "seq_selective_scan: the ring needs the convolution's inputs");
@@ -139,18 +192,35 @@ int sllm_seq_selective_scan(const sllm_seq_batch* b, const float* x, int32_t ldx
     const int longest = b->T - b->nseg + 1;                                   // no portion is longer than this
     const int chunk = std::max(1, std::min(std::min(64, longest), 10240 / per_tok));
     const size_t smem = (size_t)chunk * per_tok * sizeof(float);
-    ScanArgs p{*b, x, step_logit, B, C, z, ldx, lddt, ldb, ldc, ldz, A_log, D, inner, n_state, state, out, ldo, (uint16_t*)out16, conv_x, ld_conv, taps, ring, chunk};
-    const dim3 grid(b->nseg, blocks);
+    ScanArgs p{*b, x, step_logit, B, C, z, ldx, lddt, ldb, ldc, ldz, A_log, D, inner, n_state, state, out, ldo, (uint16_t*)out16, conv_x, ld_conv, taps, ring, chunk,
+               scratch, (longest + kScanRange - 1) / kScanRange};
     const int threads = kScanLanes * kScanChannels;
     cudaStream_t st = as_stream(stream);
     const int per_lane = (n_state + kScanLanes - 1) / kScanLanes;
-    if (per_lane <= 1) seq_selective_scan_kernel<1><<<grid, threads, smem, st>>>(p);
-    else if (per_lane <= 2) seq_selective_scan_kernel<2><<<grid, threads, smem, st>>>(p);
-    else if (per_lane <= 4) seq_selective_scan_kernel<4><<<grid, threads, smem, st>>>(p);
-    else if (per_lane <= 8) seq_selective_scan_kernel<8><<<grid, threads, smem, st>>>(p);
-    else seq_selective_scan_kernel<16><<<grid, threads, smem, st>>>(p);
-    ++g_launches;
-    SLLM_LAUNCH_CHECK();
+#define SLLM_SCAN_LAUNCH(MODE, GRID)                                                          \
+    do {                                                                                      \
+        if (per_lane <= 1) seq_selective_scan_kernel<1, MODE><<<GRID, threads, smem, st>>>(p);       \
+        else if (per_lane <= 2) seq_selective_scan_kernel<2, MODE><<<GRID, threads, smem, st>>>(p);  \
+        else if (per_lane <= 4) seq_selective_scan_kernel<4, MODE><<<GRID, threads, smem, st>>>(p);  \
+        else if (per_lane <= 8) seq_selective_scan_kernel<8, MODE><<<GRID, threads, smem, st>>>(p);  \
+        else seq_selective_scan_kernel<16, MODE><<<GRID, threads, smem, st>>>(p);                    \
+        ++g_launches;                                                                         \
+        SLLM_LAUNCH_CHECK();                                                                  \
+    } while (0)
+    // some portion spans several ranges (and the batch description numbers the query tiles): three passes
+    if (scratch && longest > kScanRange && b->seg_tile0 && b->n_qtiles > 0 && (long long)b->nseg * p.nrange <= 0x7fffffffLL) {
+        const dim3 grid(b->nseg * p.nrange, blocks);
+        SLLM_SCAN_LAUNCH(1, grid);
+        const size_t per = (size_t)inner * n_state;
+        seq_selective_scan_carry_kernel<<<dim3((unsigned)((per + 255) / 256), b->nseg), 256, 0, st>>>(p);
+        ++g_launches;
+        SLLM_LAUNCH_CHECK();
+        SLLM_SCAN_LAUNCH(2, grid);
+        return SLLM_OK;
+    }
+    const dim3 grid(b->nseg, blocks);
+    SLLM_SCAN_LAUNCH(0, grid);
+#undef SLLM_SCAN_LAUNCH
     return SLLM_OK;
 }
 

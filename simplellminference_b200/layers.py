@@ -409,6 +409,8 @@ class SelectiveScan:
     state n: S[c][n] <- exp(dt_c A[c][n]) S[c][n] + dt_c x_c B_n, y_c = sum_n S[c][n] C_n + D_c x_c; y times silu(z), then the output
     projection. State per sequence: S [inner][state] and the convolution's last taps-1 inputs (a ring indexed by position), fp32."""
 
+    scan_range = 128     # tokens of a range of the kernel's three-pass form (kScanRange of csrc/seq_ssm.cu)
+
     def __init__(self, cfg, w, pre, ops, device):
         self.cfg, self.ops = cfg, ops
         inner = cfg.inner
@@ -448,9 +450,11 @@ class SelectiveScan:
         dtl = step.scratch("scan_dt", T * inner)
         self.step(step, low.data_ptr(), L, dtl.data_ptr(), inner)
         rows16 = self.out.operand_rows(step)
+        # a portion longer than a range of the scan: per range its end state from zero and its sum of step sizes (three passes)
+        scan_ws = step.scratch("scan_ranges", step.b.n_qtiles * inner * (c.state + 1)) if T - step.nseg + 1 > self.scan_range else None
         ops.selective_scan(step.b, u.data_ptr(), inner, dtl.data_ptr(), inner, low.data_ptr() + c.dt_rank * F32B, L,
                            low.data_ptr() + (c.dt_rank + c.state) * F32B, L, z, ld, self.a_log, self.skip, inner, c.state, state["S"],
-                           None if rows16 is not None else out, inner, x, ld, c.conv, ring, step.st, out16=rows16)
+                           None if rows16 is not None else out, inner, x, ld, c.conv, ring, step.st, out16=rows16, scratch=scan_ws)
         return rows16 is not None
 
 

@@ -177,9 +177,9 @@ class Ops:
                                             dv, _p(state), _p(y), ldy, conv_x_ptr, ld_conv, channels, taps, _p(ring), st))
 
     def selective_scan(self, b, x_ptr, ldx, step_ptr, lddt, B_ptr, ldb, C_ptr, ldc, z_ptr, ldz, a_log, skip, inner, n_state, state, out, ldo, conv_x_ptr, ld_conv,
-                       taps, ring, st, out16=None):
+                       taps, ring, st, out16=None, scratch=None):
         self._ck(self.lib.sllm_seq_selective_scan(C.byref(b), x_ptr, ldx, step_ptr, lddt, B_ptr, ldb, C_ptr, ldc, z_ptr, ldz, _p(a_log), _p(skip), inner, n_state,
-                                                  _p(state), _p(out), ldo, _p(out16), conv_x_ptr, ld_conv, taps, _p(ring), st))
+                                                  _p(state), _p(out), ldo, _p(out16), conv_x_ptr, ld_conv, taps, _p(ring), _p(scratch), st))
 
     def delta_rule(self, b, q_ptr, ldq, k_ptr, ldk, v_ptr, ldv, beta_ptr, ldb, step_ptr, lda, a_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale,
                    state, o, ldo, conv_x_ptr, ldx, channels, taps, ring, st):

@@ -148,6 +148,36 @@ def test_each_mixer_alone_bf16(portions):
         assert _rel(got, want) < BF16_MIXER, (layer_cfg["mixer"], _rel(got, want))
 
 
+def test_recurrences_over_long_portions_beside_short_ones():
+    """Portions longer than a range of the scans (the recurrences then run as passes over ranges: every range from zero, a carry, every
+    range again) beside single tokens and short portions of another sequence, cut at, just before and just after the ranges' borders; the
+    state a long portion leaves is the one the next step starts from."""
+    import torch
+
+    from simplellminference_b200.seqengine import SequenceEngine
+    rng = np.random.default_rng(21)
+    d, TA, TB = 48, 700, 300
+    for layer_cfg in (L.mamba1_layer(), L.mamba1_layer(inner=70, state=1, dt_rank=1, conv=1), L.mamba1_layer(inner=33, state=20, dt_rank=7, conv=6),
+                      L.mamba1_layer(inner=8, state=100, dt_rank=3, conv=2), L.mamba2_layer(), L.mamba2_layer(heads=6, vdim=5, state=33, groups=2, norm_groups=3, conv=6)):
+        w = L.random_weights(L.make_config([layer_cfg], width=d), seed=17)
+        stub = _mixer_stub([layer_cfg], w, d)
+        ha, hb = rng.standard_normal((TA, d)).astype(np.float32), rng.standard_normal((TB, d)).astype(np.float32)
+        eng = SequenceEngine(stub, max_tokens=1280, max_seqs=2, page_len=32, graphs=False)
+        sa, sb = eng.admit(), eng.admit()
+        # (tokens of a, tokens of b) per step
+        steps = [(129, 1), (1, 128), (256, 1), (127, 130), (2, 1), (185, 39)]
+        assert sum(a for a, _ in steps) == TA and sum(b for _, b in steps) == TB
+        got_a, got_b, pa, pb = [], [], 0, 0
+        for na, nb in steps:
+            stub.h = torch.tensor(np.concatenate([ha[pa:pa + na], hb[pb:pb + nb]]), dtype=torch.float32, device=stub.device).contiguous().view(-1)
+            eng.run([(sa, np.zeros(na, np.int32), []), (sb, np.zeros(nb, np.int32), [])])
+            out = stub.outs[0].cpu().numpy()
+            got_a.append(out[:na]); got_b.append(out[na:na + nb])
+            pa, pb = pa + na, pb + nb
+        assert _rel(np.concatenate(got_a), _oracle_mixer(layer_cfg, w, ha)) < F32_TOL, layer_cfg["mixer"]
+        assert _rel(np.concatenate(got_b), _oracle_mixer(layer_cfg, w, hb)) < F32_TOL, layer_cfg["mixer"]
+
+
 def test_recurrent_state_and_rings_of_a_slot_used_again():
     """A slot that carried one sequence's state and convolution inputs serves another: its first tokens see zeros, not the old state."""
     rng = np.random.default_rng(3)
