@@ -541,11 +541,14 @@ int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, co
                         int32_t ldo, const float* conv_x, int32_t ldx, int32_t channels, int32_t taps, float* ring, sllm_stream_t stream);
 /* State-space duality (Mamba-2) per head h over each sequence, state [slots][heads][n_state][dv] fp32: dt = softplus(step_logit + dt_bias[h]),
  * S <- exp(-exp(A_log[h]) dt) S + dt B x^T, y = S^T C + skip[h] x (skip NULL = no such term); x [T][heads * dv], B and C
- * [T][groups * n_state], head h reads group h / (heads / groups). The kernel of sllm_seq_delta_rule without its correction term; ring as there. */
+ * [T][groups * n_state], head h reads group h / (heads / groups). The kernel of sllm_seq_delta_rule without its correction term; ring as there.
+ * scratch (NULL = always token by token): (n_qtiles / 4 + nseg + 1) * heads * (n_state * dv + 1) floats; with it, steps that hold a portion
+ * longer than 128 tokens run as three passes over ranges of 128 tokens (every range from zero, a carry per state element, every range again
+ * from its start state). */
 int sllm_seq_ssd_scan(const sllm_seq_batch* b, const float* x, int32_t ldx, const float* B, int32_t ldb, const float* C, int32_t ldc,
                       const float* step_logit, int32_t lda, const float* A_log, const float* dt_bias, const float* skip, int32_t heads, int32_t groups,
                       int32_t n_state, int32_t dv, float* state, float* y, int32_t ldy, const float* conv_x, int32_t ld_conv, int32_t channels,
-                      int32_t taps, float* ring, sllm_stream_t stream);
+                      int32_t taps, float* ring, float* scratch, sllm_stream_t stream);
 /* Selective scan (Mamba) per channel c over each sequence, state [slots][inner][n_state] fp32: dt = softplus(step_logit[c]),
  * S[c][n] <- exp(-dt exp(A_log[c][n])) S[c][n] + dt x[c] B[n], y[c] = sum_n S[c][n] C[n] + D[c] x[c], out = y * silu(z); B and C [T][n_state]
  * are shared by the channels. out fp32 [T][ldo] and / or out16 dense bf16 [T][inner]. ring (or NULL): the last taps-1 rows of conv_x

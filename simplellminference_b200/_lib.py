@@ -158,7 +158,7 @@ SIGNATURES.update({
     "sllm_seq_seam": (C.c_int, [_B, _P, _P, _P, _F, _I, _F, _F, _P, _I, _P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _F, _P]),
     "sllm_seq_conv_ring": (C.c_int, [_B, _P, _I, _I, _I, _P, _P, _P, _I, _P, _I, _P]),
     "sllm_seq_ring_store": (C.c_int, [_B, _P, _I, _I, _I, _P, _P]),
-    "sllm_seq_ssd_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P]),
+    "sllm_seq_ssd_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P]),
     "sllm_seq_selective_scan": (C.c_int, [_B, _P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P, _P, _I, _P, _P, _I, _I, _P, _P, _P]),
     "sllm_seq_normed_rotary_kv": (C.c_int, [_B, _P, _I, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _F, _P, _I, _I, _P, _P, _I, _P]),
     "sllm_seq_head_mix": (C.c_int, [_P, _I, _P, _I, _I, _I, _P, _I, _P, _I, _P]),

@@ -47,7 +47,17 @@ struct DeltaArgs {
     const float* conv_x; int ldx, channels, taps; float* ring;   // inputs of the convolution, stored to the ring for the next step (NULL = not)
     int chunk, PP, CB, vec;
     const float* skip;                                  // state-space form: [heads] weight of the input added to the output (NULL = none)
+    float* ws; int nrange;                              // state-space form in three passes: per range and head [dk][dv] states, then the sums of dt
 };
+
+// The state-space recurrence is linear in the state and its decay over a run of tokens is exp(-rate * (sum of the run's dt)): steps that
+// hold a long portion run it as three passes over ranges of kSsdRange tokens — every range from a zero state (end state Q, sum of dt), the
+// ranges of a portion in order per state element (start of range r+1 = exp(-rate sum_r) start_r + Q_r; the last is the sequence's new
+// state), every range again from its start state with the outputs. Ranges are numbered in segment order; segment s starts at
+// seg_tile0[s] / 4 + s (a range is four query tiles of 32 tokens, so that number never runs into the next segment's).
+constexpr int kSsdRange = 128;
+__device__ __forceinline__ size_t ssd_range_id(const sllm_seq_batch& b, int seg, int rg) { return (size_t)(b.seg_tile0[seg] / 4 + seg + rg); }
+__host__ __device__ __forceinline__ size_t ssd_range_count(int n_qtiles, int nseg) { return (size_t)(n_qtiles / 4 + nseg + 1); }
 
 // key channels of a thread: 16 for key heads of up to 512 channels (measured best of 8 / 16 / 32 at 128-wide heads), 32 for wider ones.
 // A piece's stride in shared memory is 4 floats more: 16-byte loads, pieces of the same index in different banks.
@@ -63,14 +73,19 @@ __device__ __forceinline__ void delta_cp4(void* dst, const void* src, bool take)
 }
 
 // CTA = (segment, head, block of CB value columns); thread = (value column j, piece `part` of the key channels), part = tid % PP
-// kSsd: the state-space form (no correction by the old state, no unit vectors, the step size multiplies the input)
-template <int kDeltaKP, int kMaxThreads, bool kSsd>
+// kForm 0: the delta rule. 1: the state-space form (no correction by the old state, no unit vectors, the step size multiplies the input)
+// over whole portions; 2 / 3: its first and third pass over ranges (2: from zero, no outputs; 3: from the range's start state, no state store)
+template <int kDeltaKP, int kMaxThreads, int kForm>
 __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
     constexpr int kDeltaRS = kDeltaKP + 4;
+    constexpr bool kSsd = kForm != 0, kRanges = kForm >= 2;
     extern __shared__ __align__(16) float dsm[];
     const sllm_seq_batch& b = p.b;
-    const int seg = blockIdx.x, h = blockIdx.y, kvh = h / (p.heads / p.kv_heads);
-    const int start = b.seg_start[seg], len = b.seg_len[seg], slot = b.seg_slot[seg], pos0 = b.seg_pos0[seg];
+    const int seg = kRanges ? blockIdx.x / p.nrange : blockIdx.x, rg = kRanges ? blockIdx.x % p.nrange : 0;
+    const int h = blockIdx.y, kvh = h / (p.heads / p.kv_heads);
+    const int seg_len = b.seg_len[seg], r0 = rg * kSsdRange;
+    if (kRanges && r0 >= seg_len) return;
+    const int start = b.seg_start[seg] + r0, len = kRanges ? min(kSsdRange, seg_len - r0) : seg_len, slot = b.seg_slot[seg];
     const int dk = p.dk, dv = p.dv, PP = p.PP, C = p.chunk, RS = PP * kDeltaRS, CB = p.CB;
     const int part = threadIdx.x % PP, jl = threadIdx.x / PP, j = blockIdx.z * CB + jl;   // jl: the column inside the CTA's block
     const bool live = jl < CB && j < dv;
@@ -117,13 +132,14 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    float* st = p.state + ((size_t)slot * p.heads + h) * dk * dv;
+    float* st = kRanges ? p.ws + (ssd_range_id(b, seg, rg) * p.heads + h) * dk * dv : p.state + ((size_t)slot * p.heads + h) * dk * dv;
     float S[kDeltaKP];
 #pragma unroll
     for (int x = 0; x < kDeltaKP; ++x) {
         const int kr = part * kDeltaKP + x;
-        S[x] = (live && kr < dk) ? st[(size_t)kr * dv + j] : 0.0f;
+        S[x] = (kForm != 2 && live && kr < dk) ? st[(size_t)kr * dv + j] : 0.0f;
     }
+    float dt_sum = 0.0f;
     const float rate = expf(p.A_log[h]), bias = p.dt_bias[h];
     const float skip = (kSsd && p.skip) ? p.skip[h] : 0.0f;
     issue(0, 0);
@@ -170,6 +186,19 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
         for (int i = 0; i < n; ++i) {
             const float g = s_g[i], beta = s_beta[i], kq = s_kq[i];
             const float4* kk = reinterpret_cast<const float4*>(s_k + i * RS + part * kDeltaRS);
+            if (kForm == 2) {                                                       // the end state only
+                dt_sum += beta;
+                const float u = beta * (live ? s_v[i * CB + jl] : 0.0f);
+#pragma unroll
+                for (int x = 0; x < kDeltaKP; x += 4) {
+                    const float4 kv = kk[x >> 2];
+                    S[x] = fmaf(kv.x, u, g * S[x]);
+                    S[x + 1] = fmaf(kv.y, u, g * S[x + 1]);
+                    S[x + 2] = fmaf(kv.z, u, g * S[x + 2]);
+                    S[x + 3] = fmaf(kv.w, u, g * S[x + 3]);
+                }
+                continue;
+            }
             const float4* qq = reinterpret_cast<const float4*>(s_q + i * RS + part * kDeltaRS);
             float kr[kDeltaKP];
             float d4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, e4[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // four running sums each: no long chain of dependent multiply-adds
@@ -196,25 +225,49 @@ __global__ void __launch_bounds__(kMaxThreads) seq_delta_kernel(DeltaArgs p) {
             for (int x = 0; x < kDeltaKP; ++x) S[x] = fmaf(kr[x], u, g * S[x]);
         }
         __syncthreads();
+        if (kForm != 2)
         for (int i = threadIdx.x; i < n * CB; i += blockDim.x) {
             const int col = blockIdx.z * CB + i % CB;
             if (col < dv) p.o[(size_t)(start + c0 + i / CB) * p.ldo + (size_t)h * dv + col] = s_o[i];
         }
     }
-    if (live) {
+    if (kForm != 3 && live) {
 #pragma unroll
         for (int x = 0; x < kDeltaKP; ++x) {
             const int kr = part * kDeltaKP + x;
             if (kr < dk) st[(size_t)kr * dv + j] = S[x];
         }
     }
-    if (p.ring && p.taps > 1) {          // the heads of a segment share the job of storing its last inputs of the convolution
-        const int keep = min(len, p.taps - 1);
+    if (kForm == 2 && threadIdx.x == 0 && blockIdx.z == 0)
+        p.ws[ssd_range_count(b.n_qtiles, b.nseg) * p.heads * dk * dv + ssd_range_id(b, seg, rg) * p.heads + h] = dt_sum;
+    if (kForm != 2 && p.ring && p.taps > 1 && r0 + len == seg_len) {   // the heads of a segment share the job of storing its last inputs of the convolution
+        const int seg_start = b.seg_start[seg], pos0 = b.seg_pos0[seg];
+        const int keep = min(seg_len, p.taps - 1);
         for (int i = (h * gridDim.z + blockIdx.z) * blockDim.x + threadIdx.x; i < keep * p.channels; i += p.heads * gridDim.z * blockDim.x) {
-            const int r = len - keep + i / p.channels, c = i % p.channels;
-            p.ring[((size_t)slot * (p.taps - 1) + (pos0 + r) % (p.taps - 1)) * p.channels + c] = p.conv_x[(size_t)(start + r) * p.ldx + c];
+            const int r = seg_len - keep + i / p.channels, c = i % p.channels;
+            p.ring[((size_t)slot * (p.taps - 1) + (pos0 + r) % (p.taps - 1)) * p.channels + c] = p.conv_x[(size_t)(seg_start + r) * p.ldx + c];
         }
     }
+}
+
+// thread = one state element of one head of one portion: its ranges in order, end state from zero -> start state
+__global__ void seq_ssd_carry_kernel(DeltaArgs p) {
+    const sllm_seq_batch& b = p.b;
+    const int seg = blockIdx.z, h = blockIdx.y, per = p.dk * p.dv, e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per) return;
+    const int ranges = (b.seg_len[seg] + kSsdRange - 1) / kSsdRange;
+    const float rate = expf(p.A_log[h]);
+    const float* sums = p.ws + ssd_range_count(b.n_qtiles, b.nseg) * p.heads * per;
+    float* sp = p.state + ((size_t)b.seg_slot[seg] * p.heads + h) * per + e;
+    float S = *sp;
+    for (int rg = 0; rg < ranges; ++rg) {
+        const size_t id = ssd_range_id(b, seg, rg);
+        float* qp = p.ws + (id * p.heads + h) * per + e;
+        const float Q = *qp;
+        *qp = S;
+        S = fmaf(expf(-rate * sums[id * p.heads + h]), S, Q);
+    }
+    *sp = S;
 }
 
 }  // namespace sllm
@@ -240,7 +293,7 @@ int sllm_seq_conv_ring(const sllm_seq_batch* b, const float* x, int32_t ldx, int
 static int delta_run(bool ssd, const float* skip, const sllm_seq_batch* b, const float* q, int32_t ldq, const float* k, int32_t ldk, const float* v, int32_t ldv,
                      const float* beta_logit, int32_t ldb, const float* step_logit, int32_t lda, const float* A_log, const float* dt_bias, int32_t heads,
                      int32_t kv_heads, int32_t dk, int32_t dv, float unit_eps, float qscale, float* state, float* o, int32_t ldo, const float* conv_x,
-                     int32_t ldx, int32_t channels, int32_t taps, float* ring, sllm_stream_t stream) {
+                     int32_t ldx, int32_t channels, int32_t taps, float* ring, float* scratch, sllm_stream_t stream) {
     SLLM_REQUIRE(b && b->T > 0 && b->nseg > 0 && b->seg_start && b->seg_len && b->seg_slot && b->seg_pos0, SLLM_EINVAL, "seq_delta_rule: incomplete batch description");
     SLLM_REQUIRE(q && k && v && beta_logit && step_logit && A_log && dt_bias && state && o, SLLM_EINVAL, "seq_delta_rule / seq_ssd_scan: bad argument");
     SLLM_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0, SLLM_EINVAL, "seq_delta_rule: %d heads over %d key heads", heads, kv_heads);
@@ -267,20 +320,38 @@ static int delta_run(bool ssd, const float* skip, const sllm_seq_batch* b, const
     const int longest = b->T - b->nseg + 1;                                   // no portion is longer than this
     int chunk = std::max(1, std::min(std::min(64, longest), 40960 / per_tok));
     if (tune_chunk > 0) chunk = std::max(1, std::min(tune_chunk, 50000 / per_tok));
+    // the state-space form with some portion spanning several ranges (and a batch description that numbers the query tiles): three passes.
+    // Its CTAs are many and independent: stages small enough for four of them per SM, so that one's round trips hide behind another's walk
+    // (taken while the whole-portion form would leave SMs without a CTA: the passes walk every token twice, which pays as long as the
+    // machine is not full — measured on B200 at 2048 tokens: 32 heads of 128 x 64 2.2 x faster, 64 heads equal, 128 heads 3 % slower)
+    static const int tune_ranges = getenv("SLLM_SSD_RANGES") ? atoi(getenv("SLLM_SSD_RANGES")) : -1;   // measurement aid: 0 never, 1 whenever possible
+    const bool ranges = ssd && scratch && longest > kSsdRange && b->seg_tile0 && b->n_qtiles > 0 && tune_ranges != 0 &&
+                        (tune_ranges == 1 || (long long)b->nseg * heads * blocks <= sm_count());
+    if (ranges && tune_chunk <= 0) chunk = std::max(4, std::min(chunk, 14336 / per_tok));
     const size_t smem = (size_t)chunk * per_tok * sizeof(float);
     SLLM_REQUIRE(smem <= (size_t)smem_optin_bytes() - 2048, SLLM_ENOTSUP, "seq_delta_rule: one token of a %d x %d head needs %zu bytes of shared memory", dk, dv, smem);
     const int vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0;
     DeltaArgs p{*b, q, k, v, ldq, ldk, ldv, beta_logit, step_logit, ldb, lda, A_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale, state, o, ldo,
-                conv_x, ldx, channels, taps, ring, chunk, PP, CB, vec, skip};
-#define SLLM_DELTA_LAUNCH_AS(KPV, MAXT, SSD)                                                                                                             \
-    do {                                                                                                                                                 \
-        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_delta_kernel<KPV, MAXT, SSD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        seq_delta_kernel<KPV, MAXT, SSD><<<dim3(b->nseg, heads, blocks), threads, smem, as_stream(stream)>>>(p);                                         \
+                conv_x, ldx, channels, taps, ring, chunk, PP, CB, vec, skip, scratch, (longest + kSsdRange - 1) / kSsdRange};
+    SLLM_REQUIRE(!ranges || (long long)b->nseg * p.nrange <= 0x7fffffffLL, SLLM_ENOTSUP, "seq_ssd_scan: %d portions of up to %d ranges", b->nseg, p.nrange);
+    const dim3 grid(ranges ? b->nseg * p.nrange : b->nseg, heads, blocks);
+#define SLLM_DELTA_LAUNCH_AS(KPV, MAXT, FORM)                                                                                                             \
+    do {                                                                                                                                                  \
+        if (smem > 48 * 1024) SLLM_CUDA(cudaFuncSetAttribute(seq_delta_kernel<KPV, MAXT, FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        seq_delta_kernel<KPV, MAXT, FORM><<<grid, threads, smem, as_stream(stream)>>>(p);                                                                 \
+        ++g_launches;                                                                                                                                     \
+        SLLM_LAUNCH_CHECK();                                                                                                                              \
     } while (0)
-#define SLLM_DELTA_LAUNCH(KPV, MAXT)                 \
-    do {                                             \
-        if (ssd) SLLM_DELTA_LAUNCH_AS(KPV, MAXT, true); \
-        else SLLM_DELTA_LAUNCH_AS(KPV, MAXT, false);    \
+#define SLLM_DELTA_LAUNCH(KPV, MAXT)                                                                                                  \
+    do {                                                                                                                              \
+        if (ranges) {                                                                                                                 \
+            SLLM_DELTA_LAUNCH_AS(KPV, MAXT, 2);                                                                                       \
+            seq_ssd_carry_kernel<<<dim3((dk * dv + 255) / 256, heads, b->nseg), 256, 0, as_stream(stream)>>>(p);                      \
+            ++g_launches;                                                                                                             \
+            SLLM_LAUNCH_CHECK();                                                                                                      \
+            SLLM_DELTA_LAUNCH_AS(KPV, MAXT, 3);                                                                                       \
+        } else if (ssd) SLLM_DELTA_LAUNCH_AS(KPV, MAXT, 1);                                                                           \
+        else SLLM_DELTA_LAUNCH_AS(KPV, MAXT, 0);                                                                                      \
     } while (0)
     if (KP == 8) SLLM_DELTA_LAUNCH(8, 1024);
     else if (KP == 16) SLLM_DELTA_LAUNCH(16, 512);
@@ -288,8 +359,6 @@ static int delta_run(bool ssd, const float* skip, const sllm_seq_batch* b, const
     else SLLM_DELTA_LAUNCH(32, 1024);
 #undef SLLM_DELTA_LAUNCH
 #undef SLLM_DELTA_LAUNCH_AS
-    ++g_launches;
-    SLLM_LAUNCH_CHECK();
     return SLLM_OK;
 }
 
@@ -300,15 +369,15 @@ int sllm_seq_delta_rule(const sllm_seq_batch* b, const float* q, int32_t ldq, co
                         int32_t dk, int32_t dv, float unit_eps, float qscale, float* state, float* o, int32_t ldo, const float* conv_x, int32_t ldx,
                         int32_t channels, int32_t taps, float* ring, sllm_stream_t stream) {
     return delta_run(false, nullptr, b, q, ldq, k, ldk, v, ldv, beta_logit, ldb, step_logit, lda, A_log, dt_bias, heads, kv_heads, dk, dv, unit_eps, qscale, state,
-                     o, ldo, conv_x, ldx, channels, taps, ring, stream);
+                     o, ldo, conv_x, ldx, channels, taps, ring, nullptr, stream);
 }
 
 int sllm_seq_ssd_scan(const sllm_seq_batch* b, const float* x, int32_t ldx, const float* B, int32_t ldb, const float* C, int32_t ldc, const float* step_logit,
                       int32_t lda, const float* A_log, const float* dt_bias, const float* skip, int32_t heads, int32_t groups, int32_t n_state, int32_t dv,
                       float* state, float* y, int32_t ldy, const float* conv_x, int32_t ld_conv, int32_t channels, int32_t taps, float* ring,
-                      sllm_stream_t stream) {
+                      float* scratch, sllm_stream_t stream) {
     return delta_run(true, skip, b, C, ldc, B, ldb, x, ldx, step_logit, lda, step_logit, lda, A_log, dt_bias, heads, groups, n_state, dv, 0.0f, 1.0f, state, y, ldy,
-                     conv_x, ld_conv, channels, taps, ring, stream);
+                     conv_x, ld_conv, channels, taps, ring, scratch, stream);
 }
 
 }  // extern "C"

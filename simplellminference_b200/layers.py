@@ -359,6 +359,8 @@ class StateSpaceDuality:
     in ``norm_groups`` equal parts times the weight ``norm``, then the output projection. State per sequence: S [heads][state][vdim] and
     the convolution's last taps-1 inputs (a ring indexed by position), fp32."""
 
+    scan_range = 128     # tokens of a range of the kernel's three-pass form (kSsdRange of csrc/seq_delta.cu)
+
     def __init__(self, cfg, w, pre, ops, device, eps):
         self.cfg, self.ops, self.eps = cfg, ops, eps
         self.inner = cfg.heads * cfg.vdim
@@ -395,8 +397,12 @@ class StateSpaceDuality:
         ops.conv_ring(step.b, xbc, ld, C, c.conv, self.conv_w, ring, 1, u, C, step.st, bias=self.conv_b)
         gn = c.groups * c.state
         y = step.scratch("ssd_y", T * inner)
+        # a portion longer than a range of the scan: per range and head its end state from zero and its sum of step sizes (three passes)
+        scan_ws = None
+        if T - step.nseg + 1 > self.scan_range:
+            scan_ws = step.scratch("ssd_ranges", (step.b.n_qtiles // 4 + step.nseg + 1) * c.heads * (c.state * c.vdim + 1))
         ops.ssd_scan(step.b, u.data_ptr(), C, u.data_ptr() + inner * F32B, C, u.data_ptr() + (inner + gn) * F32B, C, dt, ld, self.a_log, self.dt_bias,
-                     self.skip, c.heads, c.groups, c.state, c.vdim, state["S"], y, inner, xbc, ld, C, c.conv, ring, step.st)
+                     self.skip, c.heads, c.groups, c.state, c.vdim, state["S"], y, inner, xbc, ld, C, c.conv, ring, step.st, scratch=scan_ws)
         rows16 = self.out.operand_rows(step)       # the output projection on the tensor cores reads bf16 rows: write those, and only those
         ops.headnorm_gate(y.data_ptr(), inner, z, ld, self.norm_w, c.norm_groups, inner // c.norm_groups, self.eps, None if rows16 is not None else out, inner,
                           T, step.st, out16=rows16, gate_first=True, wide_weight=True)

@@ -172,9 +172,9 @@ class Ops:
         self._ck(self.lib.sllm_seq_ring_store(C.byref(b), x_ptr, ldx, channels, taps, _p(ring), st))
 
     def ssd_scan(self, b, x_ptr, ldx, B_ptr, ldb, C_ptr, ldc, step_ptr, lda, a_log, dt_bias, skip, heads, groups, n_state, dv, state, y, ldy, conv_x_ptr, ld_conv,
-                 channels, taps, ring, st):
+                 channels, taps, ring, st, scratch=None):
         self._ck(self.lib.sllm_seq_ssd_scan(C.byref(b), x_ptr, ldx, B_ptr, ldb, C_ptr, ldc, step_ptr, lda, _p(a_log), _p(dt_bias), _p(skip), heads, groups, n_state,
-                                            dv, _p(state), _p(y), ldy, conv_x_ptr, ld_conv, channels, taps, _p(ring), st))
+                                            dv, _p(state), _p(y), ldy, conv_x_ptr, ld_conv, channels, taps, _p(ring), _p(scratch), st))
 
     def selective_scan(self, b, x_ptr, ldx, step_ptr, lddt, B_ptr, ldb, C_ptr, ldc, z_ptr, ldz, a_log, skip, inner, n_state, state, out, ldo, conv_x_ptr, ld_conv,
                        taps, ring, st, out16=None, scratch=None):
