@@ -260,12 +260,22 @@ __global__ void seq_ssd_carry_kernel(DeltaArgs p) {
     const float* sums = p.ws + ssd_range_count(b.n_qtiles, b.nseg) * p.heads * per;
     float* sp = p.state + ((size_t)b.seg_slot[seg] * p.heads + h) * per + e;
     float S = *sp;
-    for (int rg = 0; rg < ranges; ++rg) {
-        const size_t id = ssd_range_id(b, seg, rg);
-        float* qp = p.ws + (id * p.heads + h) * per + e;
-        const float Q = *qp;
-        *qp = S;
-        S = fmaf(expf(-rate * sums[id * p.heads + h]), S, Q);
+    const size_t id0 = ssd_range_id(b, seg, 0);
+    for (int r0 = 0; r0 < ranges; r0 += 4) {               // four ranges' loads in flight before the first store
+        float Q[4], sum[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const bool has = r0 + u < ranges;
+            Q[u] = has ? p.ws[((id0 + r0 + u) * p.heads + h) * per + e] : 0.0f;
+            sum[u] = has ? sums[(id0 + r0 + u) * p.heads + h] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (r0 + u < ranges) {
+                p.ws[((id0 + r0 + u) * p.heads + h) * per + e] = S;
+                S = fmaf(expf(-rate * sum[u]), S, Q[u]);
+            }
+        }
     }
     *sp = S;
 }

@@ -163,6 +163,44 @@ __global__ void seq_headnorm_gate_kernel(const float* __restrict__ o, int ldo, c
     }
 }
 
+// the same with one CTA per (token, part), for parts too wide for a warp (a norm over a few parts of a wide row): the part's gated values
+// wait in registers between the sum of squares and the scaling, kNormPer per thread
+constexpr int kNormPer = 8;
+__global__ void __launch_bounds__(256) seq_headnorm_gate_wide_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ g, int ldg,
+                                                                     const float* __restrict__ w, int heads, int dv, float eps, float* __restrict__ out, int ldout,
+                                                                     uint16_t* __restrict__ out16, int mode) {
+    __shared__ float red[33];
+    const int t = blockIdx.x / heads, h = blockIdx.x % heads;
+    const float* orow = o + (size_t)t * ldo + (size_t)h * dv;
+    const float* grow = g + (size_t)t * ldg + (size_t)h * dv;
+    const float* wrow = (mode & 2) ? w + (size_t)h * dv : w;
+    const bool gate_first = mode & 1;
+    float v[kNormPer], sg[kNormPer];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kNormPer; ++i) {
+        const int j = threadIdx.x + i * blockDim.x;
+        v[i] = 0.0f;
+        sg[i] = 0.0f;
+        if (j < dv) {
+            const float gv = grow[j];
+            sg[i] = gv / (1.0f + expf(-gv));
+            v[i] = gate_first ? orow[j] * sg[i] : orow[j];
+            ss = fmaf(v[i], v[i], ss);
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)dv + eps);
+#pragma unroll
+    for (int i = 0; i < kNormPer; ++i) {
+        const int j = threadIdx.x + i * blockDim.x;
+        if (j < dv) {
+            const float r = gate_first ? (v[i] * inv) * wrow[j] : ((v[i] * inv) * wrow[j]) * sg[i];
+            if (out) out[(size_t)t * ldout + (size_t)h * dv + j] = r;
+            if (out16) out16[(size_t)t * heads * dv + (size_t)h * dv + j] = f32_to_bf16_bits(r);
+        }
+    }
+}
+
 // (row - mean) / sqrt(variance + eps) * w + b of one row that the CTA's threads hold strided; the variance is the mean of the squared
 // deviations (two passes: the mean first), as the definition says
 __device__ __forceinline__ void seq_layernorm_row(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, float eps,
@@ -397,7 +435,10 @@ int sllm_seq_headnorm_gate(const float* o, int32_t ldo, const float* g, int32_t 
                            int32_t ldout, void* out16, int32_t T, int32_t mode, sllm_stream_t stream) {
     SLLM_REQUIRE(o && g && w && (out || out16) && heads > 0 && dv > 0 && T > 0 && mode >= 0 && mode <= 3, SLLM_EINVAL, "seq_headnorm_gate: bad argument");
     const int items = T * heads;
-    seq_headnorm_gate_kernel<<<(items + 3) / 4, 128, 0, as_stream(stream)>>>(o, ldo, g, ldg, w, heads, dv, eps, out, ldout, (uint16_t*)out16, T, mode);
+    if (dv >= 512 && dv <= 256 * kNormPer)       // a warp per part would walk such a part in 16 and more rounds, twice
+        seq_headnorm_gate_wide_kernel<<<items, 256, 0, as_stream(stream)>>>(o, ldo, g, ldg, w, heads, dv, eps, out, ldout, (uint16_t*)out16, mode);
+    else
+        seq_headnorm_gate_kernel<<<(items + 3) / 4, 128, 0, as_stream(stream)>>>(o, ldo, g, ldg, w, heads, dv, eps, out, ldout, (uint16_t*)out16, T, mode);
     ++g_launches;
     SLLM_LAUNCH_CHECK();
     return SLLM_OK;

@@ -151,12 +151,22 @@ __global__ void seq_selective_scan_carry_kernel(ScanArgs p) {
     float* sp = p.state + (size_t)b.seg_slot[seg] * per + e;
     const float* sums = p.ws + (size_t)b.n_qtiles * per;
     float S = *sp;
-    for (int rg = 0; rg < ranges; ++rg) {
-        const size_t id = scan_range_id(b, seg, rg);
-        float* qp = p.ws + id * per + e;
-        const float Q = *qp;
-        *qp = S;
-        S = fmaf(expf(A * sums[id * p.inner + c]), S, Q);
+    const size_t id0 = scan_range_id(b, seg, 0);
+    for (int r0 = 0; r0 < ranges; r0 += 4) {               // four ranges' loads in flight before the first store
+        float Q[4], sum[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const bool has = r0 + u < ranges;
+            Q[u] = has ? p.ws[(id0 + r0 + u) * per + e] : 0.0f;
+            sum[u] = has ? sums[(id0 + r0 + u) * p.inner + c] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (r0 + u < ranges) {
+                p.ws[(id0 + r0 + u) * per + e] = S;
+                S = fmaf(expf(A * sum[u]), S, Q[u]);
+            }
+        }
     }
     *sp = S;
 }
