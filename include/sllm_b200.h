@@ -552,7 +552,7 @@ int sllm_seq_ssd_scan(const sllm_seq_batch* b, const float* x, int32_t ldx, cons
 /* Selective scan (Mamba) per channel c over each sequence, state [slots][inner][n_state] fp32: dt = softplus(step_logit[c]),
  * S[c][n] <- exp(-dt exp(A_log[c][n])) S[c][n] + dt x[c] B[n], y[c] = sum_n S[c][n] C[n] + D[c] x[c], out = y * silu(z); B and C [T][n_state]
  * are shared by the channels. out fp32 [T][ldo] and / or out16 dense bf16 [T][inner]. ring (or NULL): the last taps-1 rows of conv_x
- * [T][inner] of every portion are stored there for the convolution of the next step. n_state <= 128. scratch (NULL = always token by token):
+ * [T][inner] of every portion are stored there for the convolution of the next step. n_state <= 256. scratch (NULL = always token by token):
  * n_qtiles * inner * (n_state + 1) floats; with it, steps that hold a portion longer than 128 tokens run as three passes over ranges of 128
  * tokens (every range from zero, a carry per state element, every range again from its start state). */
 int sllm_seq_selective_scan(const sllm_seq_batch* b, const float* x, int32_t ldx, const float* step_logit, int32_t lddt, const float* B, int32_t ldb,

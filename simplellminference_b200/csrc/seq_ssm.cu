@@ -195,12 +195,12 @@ int sllm_seq_selective_scan(const sllm_seq_batch* b, const float* x, int32_t ldx
     SLLM_REQUIRE(b && b->T > 0 && b->nseg > 0 && b->seg_start && b->seg_len && b->seg_slot && b->seg_pos0, SLLM_EINVAL, "seq_selective_scan: incomplete batch description");
     SLLM_REQUIRE(x && step_logit && B && C && z && A_log && D && state && (out || out16) && inner > 0 && n_state > 0, SLLM_EINVAL, "seq_selective_scan: bad argument");
     SLLM_REQUIRE(!ring || (conv_x && taps >= 1), SLLM_EINVAL, "seq_selective_scan: the ring needs the convolution's inputs");
-    SLLM_REQUIRE(n_state <= 16 * kScanLanes, SLLM_ENOTSUP, "seq_selective_scan: %d states per channel beyond %d", n_state, 16 * kScanLanes);
+    SLLM_REQUIRE(n_state <= 32 * kScanLanes, SLLM_ENOTSUP, "seq_selective_scan: %d states per channel beyond %d", n_state, 32 * kScanLanes);
     const int blocks = (inner + kScanChannels - 1) / kScanChannels;
     SLLM_REQUIRE(blocks <= 65535, SLLM_ENOTSUP, "seq_selective_scan: %d channels", inner);
     const int per_tok = 2 * n_state + 4 * kScanChannels;
     const int longest = b->T - b->nseg + 1;                                   // no portion is longer than this
-    const int chunk = std::max(1, std::min(std::min(64, longest), 10240 / per_tok));
+    const int chunk = std::max(1, std::min(std::min(64, longest), 10240 / per_tok));   // 40 KB of stages at most
     const size_t smem = (size_t)chunk * per_tok * sizeof(float);
     ScanArgs p{*b, x, step_logit, B, C, z, ldx, lddt, ldb, ldc, ldz, A_log, D, inner, n_state, state, out, ldo, (uint16_t*)out16, conv_x, ld_conv, taps, ring, chunk,
                scratch, (longest + kScanRange - 1) / kScanRange};
@@ -213,7 +213,8 @@ int sllm_seq_selective_scan(const sllm_seq_batch* b, const float* x, int32_t ldx
         else if (per_lane <= 2) seq_selective_scan_kernel<2, MODE><<<GRID, threads, smem, st>>>(p);  \
         else if (per_lane <= 4) seq_selective_scan_kernel<4, MODE><<<GRID, threads, smem, st>>>(p);  \
         else if (per_lane <= 8) seq_selective_scan_kernel<8, MODE><<<GRID, threads, smem, st>>>(p);  \
-        else seq_selective_scan_kernel<16, MODE><<<GRID, threads, smem, st>>>(p);                    \
+        else if (per_lane <= 16) seq_selective_scan_kernel<16, MODE><<<GRID, threads, smem, st>>>(p); \
+        else seq_selective_scan_kernel<32, MODE><<<GRID, threads, smem, st>>>(p);                    \
         ++g_launches;                                                                         \
         SLLM_LAUNCH_CHECK();                                                                  \
     } while (0)

@@ -109,7 +109,7 @@ def _mixer_stub(layer_cfgs, w, width, dtype="float32", eps=EPS):
 ALONE = [L.mamba2_layer(), L.mamba2_layer(heads=1, vdim=40, state=3, groups=1, norm_groups=5, conv=1), L.mamba2_layer(heads=6, vdim=5, state=33, groups=2, norm_groups=3, conv=6),
          L.mamba2_layer(heads=2, vdim=33, state=130, groups=2, norm_groups=1, conv=2), L.mamba2_layer(heads=8, vdim=80, state=4, groups=1, norm_groups=1, conv=2),
          L.mamba2_layer(heads=16, vdim=64, state=3, groups=2, norm_groups=2, conv=3), L.mamba1_layer(), L.mamba1_layer(inner=70, state=1, dt_rank=1, conv=1),
-         L.mamba1_layer(inner=33, state=20, dt_rank=7, conv=6), L.mamba1_layer(inner=8, state=100, dt_rank=3, conv=2), L.attention_layer(),
+         L.mamba1_layer(inner=33, state=20, dt_rank=7, conv=6), L.mamba1_layer(inner=8, state=100, dt_rank=3, conv=2), L.mamba1_layer(inner=12, state=203, dt_rank=2, conv=3), L.attention_layer(),
          L.attention_layer(heads=3, kv_heads=3, dim=20, size=9, keep_first=0, rot_dims=20, conv=1), L.attention_layer(heads=8, kv_heads=1, dim=8, size=64, keep_first=10, scale=1.0, rot_dims=2),
          L.attention_layer(heads=6, kv_heads=3, dim=12, size=None, rot_dims=0, conv=5), L.attention_layer(heads=2, kv_heads=2, dim=36, size=5, keep_first=9, conv=2)]
 
