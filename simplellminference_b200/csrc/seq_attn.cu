@@ -76,16 +76,17 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs p) {
     const int seg = b.qt_seg[qt], off = b.qt_off[qt];
     const int group = p.q_heads / p.kv_heads;
     const int t0 = b.seg_start[seg] + off, pos0 = b.seg_pos0[seg] + off, slot = b.seg_slot[seg];
-    // row r of the CTA's query tile is (token t0 + r, head blockIdx.y), or with by_head (token t0, head blockIdx.y * group + r)
+    // row r of the CTA's query tile is (token t0 + r, head blockIdx.y), or with by_head (token t0, query head r of the CTA's key head)
     const int nq = p.by_head ? group : min(kBQ, b.seg_len[seg] - off);
-    const int g = p.by_head ? blockIdx.y : (blockIdx.y % p.q_heads) / group;   // key head
-    const int gv = p.cross ? blockIdx.y / p.q_heads : g;                         // value head
+    // key head and value head; with cross values and by_head the grid's y counts (value head, key head) pairs
+    const int g = p.by_head ? (int)blockIdx.y % p.kv_heads : ((int)blockIdx.y % p.q_heads) / group;
+    const int gv = p.cross ? (p.by_head ? (int)blockIdx.y / p.kv_heads : (int)blockIdx.y / p.q_heads) : g;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const KV* kp = reinterpret_cast<const KV*>(p.k_pool);
     const KV* vp = reinterpret_cast<const KV*>(p.v_pool);
     auto row_token = [&](int r) { return p.by_head ? t0 : t0 + r; };
-    auto row_head = [&](int r) { return p.by_head ? (int)blockIdx.y * group + r : (int)blockIdx.y; };                   // the result's number
-    auto row_qhead = [&](int r) { return p.by_head ? (int)blockIdx.y * group + r : (int)blockIdx.y % p.q_heads; };      // the query head behind it
+    auto row_qhead = [&](int r) { return p.by_head ? g * group + r : (int)blockIdx.y % p.q_heads; };      // the query head behind row r
+    auto row_head = [&](int r) { return p.by_head ? (p.cross ? gv * p.q_heads : 0) + g * group + r : (int)blockIdx.y; };   // the result's number
     auto row_pos = [&](int r) { return p.by_head ? pos0 : pos0 + r; };
 
     for (int i = threadIdx.x; i < kBQ * dkp; i += blockDim.x) {
@@ -615,9 +616,9 @@ int sllm_seq_attention(const sllm_seq_batch* b, const float* q, int32_t ldq, int
         SLLM_LAUNCH_CHECK();
         return SLLM_OK;
     }
-    if (b->T == b->nseg && heads / kv_heads <= kBQ && !p.cross) {   // single tokens only: the query heads of a kv head share one CTA and its tiles
+    if (b->T == b->nseg && heads / kv_heads <= kBQ) {   // single tokens only: the query heads of a kv head share one CTA and its tiles
         p.by_head = 1;
-        grid.y = kv_heads;
+        grid.y = p.cross ? kv_heads * kv_heads : kv_heads;   // with cross values: per value head too
     }
     const int chunks = dv <= 128 ? 4 : (dv <= 256 ? 8 : 16);
 #define SLLM_ATTN_LAUNCH(KV, NC)                                                                                                              \
