@@ -124,3 +124,14 @@ def test_convolutions_of_the_restatement():
     np.testing.assert_allclose(O.input_conv(h, w)[:, 0], [2, 14, 126, 238])
     np.testing.assert_allclose(O.causal_conv(h, w, [0.5])[:, 0], [1.5, 12.5, 123.5, 234.5])
     np.testing.assert_allclose(O.offset_norm(np.array([[3.0, 4.0]]), np.array([0.0, 1.0]), 0.0), [[3 / np.sqrt(12.5), 8 / np.sqrt(12.5)]])
+
+
+def test_bench_geometries_are_valid_configurations():
+    """The sizes of ``bench.py --kodezen`` parse, keep the layer pattern and differ from one another only in width and depth."""
+    from simplellminference_b200.bench_kodezen import SIZES, kodezen_config
+    from simplellminference_b200.config import KodezenConfig
+    for name, size in SIZES.items():
+        cfg = KodezenConfig.from_dict(kodezen_config(size["width"], size["repeats"]))
+        assert cfg.width == size["width"] and len(cfg.layers) == 4 * size["repeats"], name
+        assert [l.type for l in cfg.layers[:4]] == ["mamba2", "mamba1", "mamba2", "attention"]
+        assert all(l.mixer.heads * l.mixer.vdim == 2 * cfg.width for l in cfg.layers if l.type == "mamba2")
